@@ -1,0 +1,341 @@
+#!/usr/bin/env python
+"""Benchmark of the CBM product on B200: one step = one normalized product
+``Y = D^-1/2 (A+I) D^-1/2 X`` over the whole synthetic operand.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2]
+
+Workload (N = 1): copy-model graph, 100 000 nodes, p_copy = 0.7, 5 random links, degree cap 5 000,
+self loops added, alpha = 8, X = 100 000 x 500 fp32 N(0,1) — synthetic stand-in with the shape of
+the second benchmark configuration.  With N > 1 the graph has N x 100 000 nodes (same generator:
+weak scaling), its root subtrees are partitioned over the ranks, every rank holds all of X and
+computes its shard; the product itself needs no exchange, so none is timed.
+
+The JSON line reports, for the timed region, the algorithmic bytes the product must move
+(delta row pointers + delta indices + one gathered operand row per delta entry + one parent row
+per non-root row + Y written once + per-row parent/scale words) divided by time.
+
+``--impl reference`` times the reference's own CPU path for the same product on the host cores:
+``y = deltas @ x`` through torch's CSR kernel (MKL inside libtorch, the path of cbm/cbm.py:271-275)
+followed by the restated OpenMP tree update.  The reference's native module itself cannot be built
+offline (needs oneMKL headers and the arbok submodule).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the product kernel, from the ncu
+# captures summarised under profiles/ (key: workload, operand width, GPUs, scale).
+DRAM_TRAFFIC: dict = {}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (profiling captures)")
+    ap.add_argument("--f", type=int, default=0, help="override the operand width")
+    ap.add_argument("--slab", type=int, default=0)
+    ap.add_argument("--blocks", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    return ap.parse_args()
+
+
+def algorithmic_bytes(n_rows, n_delta, n_root_children, f, normalized=True):
+    """Bytes one product must move: 4(N+1) row pointers + 4 nnzD indices + 4 F nnzD gathered rows
+    + 4 F (N - roots) parent rows + 4 F N output + 8 N parent/scale words."""
+    return (4 * (n_rows + 1) + 4 * n_delta + 4 * f * n_delta + 4 * f * (n_rows - n_root_children)
+            + 4 * f * n_rows + 8 * n_rows)
+
+
+def make_workload(args, world):
+    import torch
+    from cbm4gnn_b200 import graphs
+    from cbm4gnn_b200.cbm import cbm_matrix
+    from cbm4gnn_b200.utility import add_self_loops
+    cfg = dict(graphs.CONFIGS[args.workload])
+    t0 = time.time()
+    if cfg["kind"] == "copy":
+        n = max(64, int(cfg["n"] * args.scale)) * world
+        ei = graphs.copy_model(n, cfg["p_copy"], cfg["n_random"], cfg["seed"], cfg["max_degree"])
+    else:
+        ei = graphs.make_graph(args.workload, scale=args.scale * world)
+    e = torch.from_numpy(ei)
+    if cfg["normalized"]:
+        e = add_self_loops(e)
+    t1 = time.time()
+    c = cbm_matrix(e.to(torch.int32), torch.ones(e.shape[1]), alpha=cfg["alpha"], normalized=cfg["normalized"])
+    f = args.f or cfg["f"]
+    x = graphs.make_features(args.workload, c.num_rows, f=f)
+    info = dict(workload=args.workload, n=c.num_rows, nnz=int(e.shape[1]), f=f, alpha=cfg["alpha"],
+                normalized=cfg["normalized"], n_delta=c.build_info["n_delta"],
+                n_root_children=c.build_info["n_root_children"], depth=c.build_info["depth"],
+                graph_seconds=round(t1 - t0, 2), build_seconds=round(c.build_info["seconds_total"], 3))
+    return c, x, info
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[])
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons, mx = [], set(), None
+        try:
+            for line in open(self.path):
+                p = [t.strip() for t in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    mx = float(p[2])
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            busy = [v for v in sm if mx is None or v > 0.5 * mx] or sm
+            out = dict(sm_mhz=float(np.median(busy)), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_reference(c, x, seconds, threads=None):
+    """The reference's CPU path (cbm/cbm.py:271-275) on the host: torch CSR product (MKL) + OpenMP
+    tree update; repeated for about ``seconds`` and averaged after one warm-up."""
+    import torch
+    from oracle import cbm_oracle as orc
+    threads = threads or os.cpu_count()
+    torch.set_num_threads(threads)
+    orc.clib().oracle_set_threads(threads)
+    xt = torch.from_numpy(x)
+    mr, mc = c.mst_row.numpy(), c.mst_col.numpy()
+    mult = None if c.col_multiplier is None else c.col_multiplier.numpy()
+
+    def once():
+        y = (c.deltas @ xt).numpy()
+        if mult is None:
+            orc.update(mr, mc, y, parallel=True)
+        else:
+            orc.fused_update(mr, mc, mult, y, parallel=True)
+        return y
+
+    once()
+    t0 = time.perf_counter()
+    it = 0
+    while True:
+        once()
+        it += 1
+        el = time.perf_counter() - t0
+        if el > seconds or it >= 50:
+            break
+    return el / it, it, threads
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != max(1, args.gpus) and world > 1:
+        args.gpus = world
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        c, x, info = make_workload(args, max(1, args.gpus))
+        ab = algorithmic_bytes(c.num_rows, info["n_delta"], info["n_root_children"], info["f"])
+        per, iters, threads = cpu_reference(c, x, max(5.0, args.cpu_seconds * max(1, args.steps) / 50))
+        val = ab / per / 1e9
+        line = dict(impl="reference", metric="cbm_spmm_algorithmic_GBps", value=val, unit="GB/s", n_gpus=args.gpus,
+                    steps=iters, warmup=1, ms_per_step=per * 1e3, higher_is_better=True, scaling="weak",
+                    vs_baseline=None, dtype="f32", data="synthetic",
+                    config=dict(info, l2="host run"),
+                    cpu_baseline=dict(value=val, unit="GB/s", cores=threads, kind="port",
+                                      sample=f"{iters} full products (torch CSR deltas@x + OpenMP tree update)"),
+                    e2e=dict(value=val, unit="GB/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+        print(json.dumps(line))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from cbm4gnn_b200 import _lib
+    _lib.lib()
+    c, x, info = make_workload(args, world)
+    f = info["f"]
+    if world > 1:
+        from cbm4gnn_b200.sharding import ShardedCBM
+        sh = ShardedCBM(c, rank, world, device_index=local_rank)
+        plan = sh.plan
+        xp = np.zeros((sh.part.n_labels, f), dtype=np.float32)
+        xp[sh.part.perm] = x
+        x_host = torch.from_numpy(xp).pin_memory()
+        n_out = sh.part.shard_rows
+    else:
+        plan = c.plan(local_rank)
+        x_host = torch.from_numpy(x).pin_memory()
+        n_out = c.num_rows
+    plan.tune(args.slab, args.blocks)
+    xd = x_host.to(dev, non_blocking=True)
+    yd = torch.zeros((n_out, f), device=dev)
+    y_host = torch.empty((n_out, f)).pin_memory()
+    fn = _lib.lib().cbm_b200_fused_spmm_update if c.normalized else _lib.lib().cbm_b200_spmm_update
+    stream = torch.cuda.current_stream()
+
+    def step():
+        _lib.check(fn(plan.handle, xd.data_ptr(), f, yd.data_ptr(), f, f, stream.cuda_stream))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    plan.status(stream.cuda_stream)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        step()
+        ev[i + 1].record()
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_launch = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    clocks = sampler.stop() if rank == 0 else None
+    plan.status(stream.cuda_stream)
+
+    ab_local = algorithmic_bytes(plan.n_rows, plan.n_delta, plan.n_root_children, f)
+
+    # end to end through the public API with host tensors: H2D of X, product, D2H of Y every step
+    e2e_ms = None
+    if not args.no_e2e:
+        api = (lambda: c.omp_mkl_csr_fused_spmm_update(x_host, y_host)) if c.normalized else \
+              (lambda: c.omp_mkl_csr_spmm_update(x_host, y_host))
+        if world > 1:
+            host_fn = _lib.lib().cbm_b200_spmm_update_host
+            api = lambda: _lib.check(host_fn(plan.handle, x_host.data_ptr(), y_host.data_ptr(), f,
+                                             1 if c.normalized else 0))
+        k_e2e = max(3, min(args.steps, 10))
+        api()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(k_e2e):
+            api()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / k_e2e
+        yd2 = torch.empty_like(yd)
+        _lib.check(fn(plan.handle, xd.data_ptr(), f, yd2.data_ptr(), f, f, stream.cuda_stream))
+        torch.cuda.synchronize()
+        if not torch.equal(yd2.cpu(), y_host):
+            raise SystemExit("end-to-end result differs from the device-resident result")
+
+    stats = torch.tensor([total_ms, float(ab_local), e2e_ms or 0.0, float(np.median(per_launch))],
+                         dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms_max, launch_ms = mx[0].item(), mx[2].item(), mx[3].item()
+        ab_total = sm[1].item()
+    else:
+        e2e_ms_max, launch_ms, ab_total = (e2e_ms or 0.0), stats[3].item(), float(ab_local)
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+        ms_per_step = total_ms / args.steps
+        value = ab_total / (ms_per_step * 1e-3) / 1e9
+        achieved = ab_local / (launch_ms * 1e-3) / 1e9
+        line = dict(metric="cbm_spmm_algorithmic_GBps", value=value, unit="GB/s", n_gpus=world, steps=args.steps,
+                    warmup=max(3, args.warmup), ms_per_step=ms_per_step, higher_is_better=True, scaling="weak",
+                    vs_baseline=None, dtype="f32", data="synthetic",
+                    config=dict(info, l2="operands (X + Y = %.0f MB) exceed the 126 MB L2; no flush" %
+                                ((xd.numel() + yd.numel()) * 4 / 1e6),
+                                parallelism=f"subtree-sharded x{world}" if world > 1 else "single GPU",
+                                rows_per_gpu=plan.n_rows, delta_entries_per_gpu=plan.n_delta),
+                    gpu_launches=args.steps,
+                    roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
+                                  peak_source=peak_src, traffic=None, kernel="cbm_rows_kernel",
+                                  algorithmic_bytes_per_launch=ab_local, launch_ms=launch_ms),
+                    clocks=clocks)
+        if e2e_ms is not None:
+            h2d = x_host.numel() * 4
+            d2h = y_host.numel() * 4
+            line["e2e"] = dict(value=ab_total / (e2e_ms_max * 1e-3) / 1e9, unit="GB/s", ms_per_step=e2e_ms_max,
+                               h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h)
+        if world == 1 and not args.no_cpu:
+            per, iters, threads = cpu_reference(c, x, args.cpu_seconds)
+            line["cpu_baseline"] = dict(value=ab_total / per / 1e9, unit="GB/s", ms_per_step=per * 1e3, cores=threads,
+                                        kind="port",
+                                        sample=f"{iters} full products of the same workload "
+                                               f"(torch CSR deltas@x + OpenMP tree update)")
+        line["roofline"]["traffic"] = DRAM_TRAFFIC.get((info["workload"], f, world, args.scale))
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

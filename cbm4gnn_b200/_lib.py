@@ -1,0 +1,148 @@
+"""Builds and loads ``libcbm_b200.so`` and declares its C ABI for ``ctypes``.
+
+The shared library is the only native module of the package.  It takes the place of the pybind11
+module ``cbm.cbm_mkl_cpp`` of the reference (cbm/cbm_extensions.cpp:1757-1771, built by
+cbm/setup.py:15-47 against MKL and arbok); it is compiled in-tree with ``nvcc`` for sm_100a and has
+no dependency besides the CUDA runtime and libgomp.
+
+There is deliberately no CPU fallback: if the library is missing or fails to load, every product
+entry point of the package raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import shutil
+import subprocess
+from ctypes import POINTER, c_char_p, c_double, c_float, c_int32, c_int64, c_void_p
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_ROOT = os.path.dirname(_PKG_DIR)
+LIB_PATH = os.path.join(_PKG_DIR, "libcbm_b200.so")
+SOURCES = [
+    os.path.join(_PKG_DIR, "csrc", "cbm_engine.cu"),
+    os.path.join(_PKG_DIR, "csrc", "cbm_builder.cpp"),
+]
+HEADERS = [
+    os.path.join(_ROOT, "include", "cbm_b200.h"),
+    os.path.join(_PKG_DIR, "csrc", "cbm_common.h"),
+]
+
+# Every symbol include/cbm_b200.h declares; the CPU test-suite checks the library exports all of them.
+EXPORTED = [
+    "cbm_b200_last_error",
+    "cbm_b200_version",
+    "cbm_b200_build",
+    "cbm_b200_built_info",
+    "cbm_b200_built_export_csr",
+    "cbm_b200_built_export_coo",
+    "cbm_b200_built_free",
+    "cbm_b200_plan_create",
+    "cbm_b200_plan_destroy",
+    "cbm_b200_plan_info",
+    "cbm_b200_plan_tune",
+    "cbm_b200_plan_status",
+    "cbm_b200_spmm_update",
+    "cbm_b200_fused_spmm_update",
+    "cbm_b200_update",
+    "cbm_b200_fused_update",
+    "cbm_b200_delta_spmm",
+    "cbm_b200_csr_spmm",
+    "cbm_b200_spmm_update_host",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: cannot build libcbm_b200.so")
+
+
+def needs_build() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    built = os.path.getmtime(LIB_PATH)
+    return any(os.path.getmtime(p) > built for p in SOURCES + HEADERS)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the library for sm_100a next to this file and return its path."""
+    if not force and not needs_build():
+        return LIB_PATH
+    cmd = [
+        _nvcc(), "-O3", "-std=c++17",
+        "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+        "-Xcompiler", "-fPIC,-fopenmp,-O3",
+        "-shared",
+        "-I", os.path.join(_ROOT, "include"),
+        "-I", os.path.join(_PKG_DIR, "csrc"),
+        "-o", LIB_PATH, *SOURCES, "-lgomp",
+    ]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+    if verbose:
+        print(res.stderr)
+    return LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library (built on first use when the sources are newer than the binary)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if needs_build():
+        build()
+    L = ctypes.CDLL(LIB_PATH)
+    i32p, f32p = POINTER(c_int32), POINTER(c_float)
+
+    def sig(name, restype, *argtypes):
+        fn = getattr(L, name)
+        fn.restype = restype
+        fn.argtypes = list(argtypes)
+
+    sig("cbm_b200_last_error", c_char_p)
+    sig("cbm_b200_version", c_char_p)
+    sig("cbm_b200_build", c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int32,
+        POINTER(c_void_p))
+    sig("cbm_b200_built_info", c_int32, c_void_p, POINTER(c_int64), POINTER(c_int64), i32p, i32p,
+        POINTER(c_double))
+    sig("cbm_b200_built_export_csr", c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p)
+    sig("cbm_b200_built_export_coo", c_int32, c_void_p, c_void_p, c_void_p, c_void_p)
+    sig("cbm_b200_built_free", None, c_void_p)
+    sig("cbm_b200_plan_create", c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, POINTER(c_void_p))
+    sig("cbm_b200_plan_destroy", None, c_void_p)
+    sig("cbm_b200_plan_info", c_int32, c_void_p, i32p, POINTER(c_int64), i32p, i32p,
+        POINTER(c_int64))
+    sig("cbm_b200_plan_tune", c_int32, c_void_p, c_int32, c_int32)
+    sig("cbm_b200_plan_status", c_int32, c_void_p, c_void_p)
+    for name in ("cbm_b200_spmm_update", "cbm_b200_fused_spmm_update", "cbm_b200_delta_spmm"):
+        sig(name, c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p)
+    for name in ("cbm_b200_update", "cbm_b200_fused_update"):
+        sig(name, c_int32, c_void_p, c_void_p, c_int64, c_int32, c_void_p)
+    sig("cbm_b200_csr_spmm", c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_int64, c_void_p, c_int64, c_int32, c_void_p)
+    sig("cbm_b200_spmm_update_host", c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32)
+    _lib = L
+    return L
+
+
+def check(status: int) -> None:
+    """Raise ``RuntimeError`` carrying the library's message for a non-zero status.
+
+    The reference turns dtype errors into ``RuntimeError`` through ``TORCH_CHECK``
+    (cbm/cbm_extensions.cpp:659-666) and kills the process on MKL errors (cbm/helpers.hpp:57-85);
+    here every native failure surfaces as ``RuntimeError``.
+    """
+    if status != 0:
+        msg = lib().cbm_b200_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"cbm_b200 error {status}: {msg}")

@@ -1,0 +1,801 @@
+// CUDA engine (sm_100a) for the CBM product: plans, kernels and the compute half of the C ABI.
+//
+// What the reference does in two steps per call — an MKL sparse product dst = deltas * rhs
+// (cbm/cbm_extensions.cpp:694-704) followed by a depth-first walk that adds every finished parent
+// row into its children (cbm/cbm_extensions.cpp:1166-1218; normalized form :1285-1373) — is done
+// here by ONE kernel.  Rows are issued to warps in a topological order of the tree.  A warp
+//   1. gathers the signed rows of X named by its row's delta entries into registers,
+//   2. waits (bounded) until its parent's finished row is published, reads it from L2,
+//   3. applies the row scale, stores the finished row once, and publishes it.
+// Step 1 does not depend on the parent, so the wait in step 2 is normally already satisfied.
+// The dense operand is processed in column slabs so that one slab of X stays resident in the
+// 126 MB L2 while every row gathers from it.
+//
+// Forward progress: work items are claimed in increasing order from one counter, and an item only
+// ever waits for an item with a smaller index.  Whoever holds that smaller item is already running
+// and, by induction, never blocked on anything unclaimed, so the kernel cannot deadlock however
+// many thread blocks are resident.  Every wait is bounded all the same: when the bound runs out
+// the warp raises the plan's status word and all warps drain.
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "cbm_b200.h"
+#include "cbm_common.h"
+
+namespace cbm {
+std::string& last_error_slot() {
+    static thread_local std::string slot;
+    return slot;
+}
+}  // namespace cbm
+
+extern "C" const char* cbm_b200_last_error(void) { return cbm::last_error_slot().c_str(); }
+extern "C" const char* cbm_b200_version(void) { return "cbm_b200 0.1 sm_100a"; }
+
+namespace {
+
+using i32 = int32_t;
+using i64 = int64_t;
+using u64 = unsigned long long;
+
+#define CBM_CUDA(call)                                                                      \
+    do {                                                                                    \
+        cudaError_t e__ = (call);                                                           \
+        if (e__ != cudaSuccess)                                                             \
+            return cbm::fail(CBM_B200_ERR_CUDA, std::string(#call) + ": " +                 \
+                                                    cudaGetErrorString(e__));               \
+    } while (0)
+
+// One row of the schedule, in processing order.  32 bytes, read as two 16-byte loads.
+struct __align__(16) RowDesc {
+    i32 out_row;      // row of y this item produces (local to the shard)
+    i32 parent_row;   // row of y holding the parent's finished row, -1 under the virtual root
+    i32 parent_pos;   // parent's position in processing order (index of its ready flag)
+    i32 has_children; // non-zero: someone will wait for this row
+    i32 beg, end;     // delta entries of the row in the plan's col/val arrays
+    float scale;      // s_v  = D^-1/2 of this row (1 when the plan has no multiplier)
+    float inv_parent; // 1/s_u of the parent (1 when none)
+};
+
+enum Mode : int { MODE_FUSED = 0, MODE_DELTA_ONLY = 1, MODE_UPDATE_ONLY = 2 };
+
+struct KParams {
+    const RowDesc* desc;
+    const i32* col;
+    const float* val;
+    const float* x;
+    float* y;
+    i64 ldx, ldy;
+    i32 f;
+    i32 slab_w;     // columns per slab
+    i32 n_rows;     // rows computed by this plan
+    i64 n_units;    // n_rows * n_slabs
+    i32 chunk;      // units claimed per counter increment
+    u64 n_chunks;
+    u64* counter;   // [0] next chunk to claim, [1] warps that have left; both 0 between launches
+    u64 n_warps;    // warps in this launch
+    i32* flags;     // n_slabs * n_rows ready flags holding the epoch of the launch that set them
+    i32 epoch;
+    i32* status;    // 0 ok; non-zero: a wait gave up
+    i32 mode;
+    i32 use_scale;
+    u64 wait_ns;
+};
+
+__device__ __forceinline__ i32 ld_acquire(const i32* p) {
+    i32 v;
+    asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release(i32* p, i32 v) {
+    asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ i32 ld_relaxed(const i32* p) {
+    i32 v;
+    asm volatile("ld.relaxed.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ u64 global_ns() {
+    u64 t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait for `*flag == epoch`.  All lanes of the warp call it together.
+__device__ __forceinline__ bool wait_ready(const i32* flag, i32 epoch, i32* status, u64 wait_ns) {
+    if (ld_acquire(flag) == epoch) return true;
+    const u64 t0 = global_ns();
+    unsigned spins = 0;
+    for (;;) {
+        if (ld_acquire(flag) == epoch) return true;
+        ++spins;
+        if ((spins & 31u) == 0) {
+            if (ld_relaxed(status) != 0) return false;  // someone else gave up: drain
+            if (global_ns() - t0 > wait_ns) {
+                atomicExch(status, CBM_B200_ERR_TIMEOUT);
+                return false;
+            }
+        }
+        __nanosleep(spins < 16 ? 20 : 200);
+    }
+}
+
+template <bool V4>
+struct Vec;
+template <>
+struct Vec<true> {
+    using T = float4;
+    static constexpr int E = 4;
+    static __device__ __forceinline__ T zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+    static __device__ __forceinline__ T ld_ro(const float* p) { return __ldg((const float4*)p); }
+    static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg((const float4*)p); }
+    static __device__ __forceinline__ void st(float* p, T v) { *(float4*)p = v; }
+    static __device__ __forceinline__ T fma(float w, T a, T c) {
+        c.x = fmaf(w, a.x, c.x);
+        c.y = fmaf(w, a.y, c.y);
+        c.z = fmaf(w, a.z, c.z);
+        c.w = fmaf(w, a.w, c.w);
+        return c;
+    }
+    static __device__ __forceinline__ T mul(float w, T a) {
+        a.x *= w;
+        a.y *= w;
+        a.z *= w;
+        a.w *= w;
+        return a;
+    }
+};
+template <>
+struct Vec<false> {
+    using T = float;
+    static constexpr int E = 1;
+    static __device__ __forceinline__ T zero() { return 0.f; }
+    static __device__ __forceinline__ T ld_ro(const float* p) { return __ldg(p); }
+    static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg(p); }
+    static __device__ __forceinline__ void st(float* p, T v) { *p = v; }
+    static __device__ __forceinline__ T fma(float w, T a, T c) { return fmaf(w, a, c); }
+    static __device__ __forceinline__ T mul(float w, T a) { return w * a; }
+};
+
+// acc[v] += sum over entries [beg,end) of val * X[col, c0 + lane_off(v) ...]
+template <int NV, bool V4>
+__device__ __forceinline__ void gather_row(const i32* __restrict__ col,
+                                           const float* __restrict__ val, i32 beg, i32 end,
+                                           const float* __restrict__ xs, i64 ldx,
+                                           const bool (&ok)[NV], typename Vec<V4>::T (&acc)[NV],
+                                           int lane) {
+    using V = Vec<V4>;
+    using T = typename V::T;
+    constexpr int STEP = 32 * V::E;
+    for (i32 b = beg; b < end; b += 32) {
+        const i32 n_here = min(32, end - b);
+        i32 mc = 0;
+        float mw = 0.f;
+        if (lane < n_here) {
+            mc = __ldg(col + b + lane);
+            mw = __ldg(val + b + lane);
+        }
+        i32 j = 0;
+        for (; j + 4 <= n_here; j += 4) {
+            i32 c[4];
+            float w[4];
+            T t[4][NV];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                c[k] = __shfl_sync(0xffffffffu, mc, j + k);
+                w[k] = __shfl_sync(0xffffffffu, mw, j + k);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float* r = xs + (i64)c[k] * ldx;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) t[k][v] = ok[v] ? V::ld_ro(r + v * STEP) : V::zero();
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+#pragma unroll
+                for (int v = 0; v < NV; ++v) acc[v] = V::fma(w[k], t[k][v], acc[v]);
+        }
+        for (; j < n_here; ++j) {
+            const i32 c = __shfl_sync(0xffffffffu, mc, j);
+            const float w = __shfl_sync(0xffffffffu, mw, j);
+            const float* r = xs + (i64)c * ldx;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if (ok[v]) acc[v] = V::fma(w, V::ld_ro(r + v * STEP), acc[v]);
+        }
+    }
+}
+
+// A warp signs off; the last one out rewinds both counters for the next launch.  This holds on
+// the drain path after a failed wait too, so a plan stays usable after a timeout.
+__device__ __forceinline__ void leave(const KParams& p, int lane) {
+    if (lane == 0) {
+        if (atomicAdd(p.counter + 1, 1ULL) == p.n_warps - 1) {
+            p.counter[0] = 0;
+            p.counter[1] = 0;
+            __threadfence();
+        }
+    }
+}
+
+// The fused product kernel.  One warp per (row, column slab) item; NV vectors per lane.
+template <int NV, bool V4>
+__global__ void __launch_bounds__(256) cbm_rows_kernel(const KParams p) {
+    using V = Vec<V4>;
+    using T = typename V::T;
+    constexpr int STEP = 32 * V::E;
+    const int lane = threadIdx.x & 31;
+
+    for (;;) {
+        u64 t = 0;
+        if (lane == 0) t = atomicAdd(p.counter, 1ULL);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t >= p.n_chunks) {
+            leave(p, lane);
+            return;
+        }
+        const i64 u0 = (i64)t * p.chunk;
+        const i64 u1 = min(u0 + (i64)p.chunk, p.n_units);
+        for (i64 u = u0; u < u1; ++u) {
+            const i32 slab = (i32)(u / p.n_rows);
+            const i32 pos = (i32)(u - (i64)slab * p.n_rows);
+            const int4 da = __ldg((const int4*)(p.desc + pos));
+            const int4 db = __ldg((const int4*)(p.desc + pos) + 1);
+            const i32 out_row = da.x, parent_row = da.y, parent_pos = da.z, has_children = da.w;
+            const i32 beg = db.x, end = db.y;
+            const float scale = __int_as_float(db.z), inv_parent = __int_as_float(db.w);
+
+            const i32 c0 = slab * p.slab_w;
+            const i32 wcols = min(p.slab_w, p.f - c0);
+            const i32 lane_col = c0 + lane * V::E;
+            bool ok[NV];
+#pragma unroll
+            for (int v = 0; v < NV; ++v) ok[v] = (lane * V::E + v * STEP) < wcols;
+
+            T acc[NV];
+            float* yrow = p.y + (i64)out_row * p.ldy + lane_col;
+            if (p.mode == MODE_UPDATE_ONLY) {
+#pragma unroll
+                for (int v = 0; v < NV; ++v) acc[v] = ok[v] ? V::ld_l2(yrow + v * STEP) : V::zero();
+            } else {
+#pragma unroll
+                for (int v = 0; v < NV; ++v) acc[v] = V::zero();
+                gather_row<NV, V4>(p.col, p.val, beg, end, p.x + lane_col, p.ldx, ok, acc, lane);
+            }
+
+            if (p.mode != MODE_DELTA_ONLY) {
+                if (parent_row >= 0) {
+                    if (!wait_ready(p.flags + (i64)slab * p.n_rows + parent_pos, p.epoch, p.status,
+                                    p.wait_ns)) {
+                        leave(p, lane);
+                        return;
+                    }
+                    const float* prow = p.y + (i64)parent_row * p.ldy + lane_col;
+                    const float ip = p.use_scale ? inv_parent : 1.0f;
+#pragma unroll
+                    for (int v = 0; v < NV; ++v)
+                        if (ok[v]) acc[v] = V::fma(ip, V::ld_l2(prow + v * STEP), acc[v]);
+                }
+                if (p.use_scale) {
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) acc[v] = V::mul(scale, acc[v]);
+                }
+            }
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if (ok[v]) V::st(yrow + v * STEP, acc[v]);
+
+            if (has_children && p.mode != MODE_DELTA_ONLY) {
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) st_release(p.flags + (i64)slab * p.n_rows + pos, p.epoch);
+            }
+        }
+    }
+}
+
+// Plain CSR product (no tree): rows in natural order, one warp per (row, slab), grid-stride.
+template <int NV, bool V4>
+__global__ void __launch_bounds__(256)
+    csr_rows_kernel(i32 n_rows, const i32* __restrict__ row_b, const i32* __restrict__ row_e,
+                    const i32* __restrict__ col, const float* __restrict__ val,
+                    const float* __restrict__ x, i64 ldx, float* __restrict__ y, i64 ldy, i32 f,
+                    i32 slab_w, i64 n_units) {
+    using V = Vec<V4>;
+    using T = typename V::T;
+    constexpr int STEP = 32 * V::E;
+    const int lane = threadIdx.x & 31;
+    const i64 warp = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const i64 n_warps = ((i64)gridDim.x * blockDim.x) >> 5;
+    for (i64 u = warp; u < n_units; u += n_warps) {
+        const i32 slab = (i32)(u / n_rows);
+        const i32 row = (i32)(u - (i64)slab * n_rows);
+        const i32 c0 = slab * slab_w;
+        const i32 wcols = min(slab_w, f - c0);
+        const i32 lane_col = c0 + lane * V::E;
+        bool ok[NV];
+        T acc[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            ok[v] = (lane * V::E + v * STEP) < wcols;
+            acc[v] = V::zero();
+        }
+        gather_row<NV, V4>(col, val, __ldg(row_b + row), __ldg(row_e + row), x + lane_col, ldx, ok,
+                           acc, lane);
+        float* yrow = y + (i64)row * ldy + lane_col;
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+            if (ok[v]) V::st(yrow + v * STEP, acc[v]);
+    }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Picks the widest vector form the operands allow and the slab width it covers.
+struct Shape {
+    bool v4;
+    int nv;
+    i32 slab_w;
+    i32 n_slabs;
+};
+Shape pick_shape(i32 f, i32 want_slab, bool can_v4) {
+    Shape s{};
+    s.v4 = can_v4;
+    const i32 lane_w = s.v4 ? 128 : 32;  // columns covered by one vector per lane
+    i32 slab = want_slab > 0 ? want_slab : (s.v4 ? 128 : 64);
+    slab = std::max(lane_w, (slab / lane_w) * lane_w);
+    slab = std::min(slab, lane_w * 4);
+    const i32 f_up = ((f + lane_w - 1) / lane_w) * lane_w;
+    slab = std::min(slab, f_up);
+    s.nv = slab / lane_w;
+    if (s.nv == 3) {
+        s.nv = 2;
+        slab = 2 * lane_w;
+    }
+    s.slab_w = slab;
+    s.n_slabs = (f + slab - 1) / slab;
+    return s;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+struct cbm_b200_plan {
+    int device = 0;
+    i32 n = 0;
+    i32 n_labels = 0;  // rows of the dense right-hand side
+    i32 n_out = 0;     // rows of the output shard (owned label range)
+    i32 n_rows = 0;    // rows actually computed
+    i64 n_delta = 0;
+    i32 n_root_children = 0;
+    i32 depth = 0;
+    bool normalized = false;
+    RowDesc* d_desc = nullptr;
+    i32* d_col = nullptr;
+    float* d_val = nullptr;
+    i32* d_flags = nullptr;
+    i64 flags_cap = 0;
+    u64* d_counter = nullptr;
+    i32* d_status = nullptr;
+    i32 epoch = 0;
+    i32 slab_width = 0;
+    i32 n_blocks = 0;
+    i32 sm_count = 148;
+    i64 device_bytes = 0;
+    cudaStream_t own_stream = nullptr;
+    float* stage_x = nullptr;
+    float* stage_y = nullptr;
+    i64 stage_x_cap = 0, stage_y_cap = 0;
+};
+
+namespace {
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+template <class T>
+int upload(T** dst, const std::vector<T>& src, i64& bytes) {
+    *dst = nullptr;
+    const size_t sz = std::max<size_t>(src.size(), 1) * sizeof(T);
+    CBM_CUDA(cudaMalloc((void**)dst, sz));
+    bytes += (i64)sz;
+    if (!src.empty())
+        CBM_CUDA(cudaMemcpy(*dst, src.data(), src.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return CBM_B200_OK;
+}
+
+}  // namespace
+
+extern "C" void cbm_b200_plan_destroy(cbm_b200_plan* p) {
+    if (!p) return;
+    DeviceGuard g(p->device);
+    cudaFree(p->d_desc);
+    cudaFree(p->d_col);
+    cudaFree(p->d_val);
+    cudaFree(p->d_flags);
+    cudaFree(p->d_counter);
+    cudaFree(p->d_status);
+    cudaFree(p->stage_x);
+    cudaFree(p->stage_y);
+    if (p->own_stream) cudaStreamDestroy(p->own_stream);
+    delete p;
+}
+
+extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int32_t* mst_col,
+                                    const int32_t* delta_crow, const int32_t* delta_col,
+                                    const float* delta_val, const float* multiplier,
+                                    const int32_t* perm, int32_t n_labels, int32_t own_begin,
+                                    int32_t own_end, int32_t device, cbm_b200_plan** out) {
+    if (!out) return cbm::fail(CBM_B200_ERR_ARG, "plan_create: out is NULL");
+    *out = nullptr;
+    if (n < 0 || !mst_row || !delta_crow || (n > 0 && !mst_col))
+        return cbm::fail(CBM_B200_ERR_ARG, "plan_create: NULL tree or delta arrays");
+    if (n_labels == 0) n_labels = n;
+    if (n_labels < n || (!perm && n_labels != n))
+        return cbm::fail(CBM_B200_ERR_ARG, "plan_create: n_labels must be >= n (== n without perm)");
+    if (own_begin < 0 || own_end > n_labels || own_begin > own_end)
+        return cbm::fail(CBM_B200_ERR_ARG, "plan_create: bad owned range");
+    const i64 nd_all = delta_crow[n];
+    if (nd_all > 0 && (!delta_col || !delta_val))
+        return cbm::fail(CBM_B200_ERR_ARG, "plan_create: NULL delta col/val");
+
+    // ---- validate the tree: every row exactly once, reachable from the virtual root ----
+    if (mst_row[0] != 0 || mst_row[n + 1] != n)
+        return cbm::fail(CBM_B200_ERR_FORMAT, "plan_create: mst_row must run from 0 to n");
+    std::vector<i32> parent((size_t)n, -1);
+    for (i32 u = 0; u <= n; ++u) {
+        if (mst_row[u] > mst_row[u + 1])
+            return cbm::fail(CBM_B200_ERR_FORMAT, "plan_create: mst_row not monotone");
+        for (i32 k = mst_row[u]; k < mst_row[u + 1]; ++k) {
+            const i32 v = mst_col[k];
+            if (v < 0 || v >= n || parent[v] != -1 || v == u)
+                return cbm::fail(CBM_B200_ERR_FORMAT,
+                                 "plan_create: mst_col is not a tree over the rows");
+            parent[v] = u;
+        }
+    }
+    std::vector<i32> order;  // breadth-first from the virtual root
+    order.reserve((size_t)n);
+    std::vector<i32> level((size_t)n + 1, 0);
+    {
+        std::vector<i32> q;
+        q.reserve((size_t)n + 1);
+        q.push_back(n);
+        for (size_t h = 0; h < q.size(); ++h) {
+            const i32 u = q[h];
+            for (i32 k = mst_row[u]; k < mst_row[u + 1]; ++k) {
+                level[mst_col[k]] = level[u] + 1;
+                q.push_back(mst_col[k]);
+            }
+        }
+        if ((i32)q.size() != n + 1)
+            return cbm::fail(CBM_B200_ERR_FORMAT, "plan_create: tree has a cycle or unreachable rows");
+        order.assign(q.begin() + 1, q.end());
+    }
+    for (i32 v = 0; v < n; ++v) {
+        if (delta_crow[v] > delta_crow[v + 1] || delta_crow[v] < 0)
+            return cbm::fail(CBM_B200_ERR_FORMAT, "plan_create: delta_crow not monotone");
+    }
+    for (i64 k = 0; k < nd_all; ++k)
+        if (delta_col[k] < 0 || delta_col[k] >= n)
+            return cbm::fail(CBM_B200_ERR_FORMAT, "plan_create: delta column out of range");
+    if (perm) {
+        std::vector<char> seen((size_t)n_labels, 0);
+        for (i32 v = 0; v < n; ++v) {
+            if (perm[v] < 0 || perm[v] >= n_labels || seen[perm[v]])
+                return cbm::fail(CBM_B200_ERR_ARG, "plan_create: perm labels not distinct / in range");
+            seen[perm[v]] = 1;
+        }
+    }
+    auto label = [&](i32 v) { return perm ? perm[v] : v; };
+    auto owned = [&](i32 v) {
+        const i32 l = label(v);
+        return l >= own_begin && l < own_end;
+    };
+
+    // ---- schedule: owned rows in breadth-first order ----
+    std::vector<i32> pos_of((size_t)n, -1);
+    std::vector<RowDesc> desc;
+    desc.reserve((size_t)(own_end - own_begin));
+    std::vector<i32> pcol;
+    std::vector<float> pval;
+    i32 depth = 0, n_root_children = 0;
+    for (i32 v : order) {
+        if (!owned(v)) continue;
+        const i32 u = parent[v];
+        if (u != n && !owned(u))
+            return cbm::fail(CBM_B200_ERR_ARG,
+                             "plan_create: owned range cuts a subtree (parent of an owned row "
+                             "is not owned)");
+        RowDesc d{};
+        d.out_row = label(v) - own_begin;
+        d.parent_row = (u == n) ? -1 : label(u) - own_begin;
+        d.parent_pos = (u == n) ? -1 : pos_of[u];
+        d.has_children = 0;
+        d.beg = (i32)pcol.size();
+        for (i32 k = delta_crow[v]; k < delta_crow[v + 1]; ++k) {
+            pcol.push_back(label(delta_col[k]));
+            pval.push_back(delta_val[k]);
+        }
+        d.end = (i32)pcol.size();
+        d.scale = multiplier ? multiplier[v] : 1.0f;
+        d.inv_parent = (multiplier && u != n) ? 1.0f / multiplier[u] : 1.0f;
+        pos_of[v] = (i32)desc.size();
+        if (u != n) desc[pos_of[u]].has_children = 1;
+        else ++n_root_children;
+        depth = std::max(depth, level[v]);
+        desc.push_back(d);
+    }
+
+    int n_dev = 0;
+    CBM_CUDA(cudaGetDeviceCount(&n_dev));
+    if (device < 0 || device >= n_dev)
+        return cbm::fail(CBM_B200_ERR_ARG, "plan_create: no such CUDA device");
+    DeviceGuard guard(device);
+    if (!guard.ok) return cbm::fail(CBM_B200_ERR_CUDA, "plan_create: cudaSetDevice failed");
+
+    cbm_b200_plan* p = new (std::nothrow) cbm_b200_plan();
+    if (!p) return cbm::fail(CBM_B200_ERR_ALLOC, "plan_create: out of host memory");
+    p->device = device;
+    p->n = n;
+    p->n_labels = n_labels;
+    p->n_out = own_end - own_begin;
+    p->n_rows = (i32)desc.size();
+    p->n_delta = (i64)pcol.size();
+    p->n_root_children = n_root_children;
+    p->depth = depth;
+    p->normalized = multiplier != nullptr;
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) p->sm_count = prop.multiProcessorCount;
+    int rc = upload(&p->d_desc, desc, p->device_bytes);
+    if (rc == CBM_B200_OK) rc = upload(&p->d_col, pcol, p->device_bytes);
+    if (rc == CBM_B200_OK) rc = upload(&p->d_val, pval, p->device_bytes);
+    if (rc == CBM_B200_OK) {
+        cudaError_t e = cudaMalloc((void**)&p->d_counter, 2 * sizeof(u64));
+        if (e == cudaSuccess) e = cudaMemset(p->d_counter, 0, 2 * sizeof(u64));
+        if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_status, sizeof(i32));
+        if (e == cudaSuccess) e = cudaMemset(p->d_status, 0, sizeof(i32));
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess)
+            rc = cbm::fail(CBM_B200_ERR_CUDA, std::string("plan_create: ") + cudaGetErrorString(e));
+        p->device_bytes += 16;
+    }
+    if (rc != CBM_B200_OK) {
+        const std::string keep = cbm::last_error_slot();
+        cbm_b200_plan_destroy(p);
+        cbm::last_error_slot() = keep;
+        return rc;
+    }
+    *out = p;
+    return CBM_B200_OK;
+}
+
+extern "C" int cbm_b200_plan_info(const cbm_b200_plan* p, int32_t* n_rows, int64_t* n_delta,
+                                  int32_t* n_root_children, int32_t* depth,
+                                  int64_t* device_bytes) {
+    if (!p) return cbm::fail(CBM_B200_ERR_ARG, "plan_info: NULL plan");
+    if (n_rows) *n_rows = p->n_rows;
+    if (n_delta) *n_delta = p->n_delta;
+    if (n_root_children) *n_root_children = p->n_root_children;
+    if (depth) *depth = p->depth;
+    if (device_bytes) *device_bytes = p->device_bytes;
+    return CBM_B200_OK;
+}
+
+extern "C" int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t n_blocks) {
+    if (!p) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: NULL plan");
+    if (slab_width < 0 || n_blocks < 0) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: negative knob");
+    p->slab_width = slab_width;
+    p->n_blocks = n_blocks;
+    return CBM_B200_OK;
+}
+
+extern "C" int cbm_b200_plan_status(cbm_b200_plan* p, void* stream) {
+    if (!p) return cbm::fail(CBM_B200_ERR_ARG, "plan_status: NULL plan");
+    DeviceGuard g(p->device);
+    CBM_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    i32 st = 0;
+    CBM_CUDA(cudaMemcpy(&st, p->d_status, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        CBM_CUDA(cudaMemset(p->d_status, 0, sizeof(i32)));
+        return cbm::fail(CBM_B200_ERR_TIMEOUT,
+                         "a bounded wait for a parent row ran out; the last product is invalid");
+    }
+    return CBM_B200_OK;
+}
+
+namespace {
+
+template <int NV, bool V4>
+int launch_rows(const KParams& kp, int blocks, cudaStream_t s) {
+    cbm_rows_kernel<NV, V4><<<blocks, 256, 0, s>>>(kp);
+    CBM_CUDA(cudaGetLastError());
+    return CBM_B200_OK;
+}
+
+int check_dense(const char* who, const void* x, i64 ldx, const void* y, i64 ldy, i32 f) {
+    if (f <= 0) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": f must be positive");
+    if (!y || ldy < f) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": bad y / ldy");
+    if (x && ldx < f) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": ldx < f");
+    if (x && x == y) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": x and y alias");
+    return CBM_B200_OK;
+}
+
+int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* y, i64 ldy, i32 f,
+             int mode, bool use_scale, cudaStream_t s) {
+    if (!p) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": NULL plan");
+    int rc = check_dense(who, x, ldx, y, ldy, f);
+    if (rc) return rc;
+    if (mode != MODE_UPDATE_ONLY && !x)
+        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": x is NULL");
+    if (use_scale && !p->normalized)
+        return cbm::fail(CBM_B200_ERR_ARG,
+                         std::string(who) + ": plan was created without a multiplier");
+    if (p->n_rows == 0) return CBM_B200_OK;
+    DeviceGuard g(p->device);
+
+    const bool can_v4 = (f % 4 == 0) && (ldy % 4 == 0) && aligned16(y) &&
+                        (mode == MODE_UPDATE_ONLY || ((ldx % 4 == 0) && aligned16(x)));
+    const Shape sh = pick_shape(f, p->slab_width, can_v4);
+
+    const i64 need_flags = (i64)sh.n_slabs * p->n_rows;
+    if (need_flags > p->flags_cap) {
+        // Growing the flag array: the old one may still be read by a launch in flight.
+        CBM_CUDA(cudaStreamSynchronize(s));
+        cudaFree(p->d_flags);
+        p->d_flags = nullptr;
+        p->device_bytes -= p->flags_cap * (i64)sizeof(i32);
+        p->flags_cap = 0;
+        CBM_CUDA(cudaMalloc((void**)&p->d_flags, (size_t)need_flags * sizeof(i32)));
+        CBM_CUDA(cudaMemset(p->d_flags, 0, (size_t)need_flags * sizeof(i32)));
+        p->flags_cap = need_flags;
+        p->device_bytes += need_flags * (i64)sizeof(i32);
+    }
+    if (p->epoch == INT32_MAX) {  // epochs exhausted: start over on clean flags
+        CBM_CUDA(cudaMemsetAsync(p->d_flags, 0, (size_t)p->flags_cap * sizeof(i32), s));
+        p->epoch = 0;
+    }
+
+    KParams kp{};
+    kp.desc = p->d_desc;
+    kp.col = p->d_col;
+    kp.val = p->d_val;
+    kp.x = x;
+    kp.y = y;
+    kp.ldx = ldx;
+    kp.ldy = ldy;
+    kp.f = f;
+    kp.slab_w = sh.slab_w;
+    kp.n_rows = p->n_rows;
+    kp.n_units = need_flags;
+    kp.chunk = 4;
+    kp.n_chunks = (u64)((kp.n_units + kp.chunk - 1) / kp.chunk);
+    kp.counter = p->d_counter;
+    kp.flags = p->d_flags;
+    kp.epoch = ++p->epoch;
+    kp.status = p->d_status;
+    kp.mode = mode;
+    kp.use_scale = use_scale ? 1 : 0;
+    kp.wait_ns = 2000000000ULL;
+
+    int blocks = p->n_blocks > 0 ? p->n_blocks : p->sm_count * 8;
+    const i64 max_useful = (i64)((kp.n_chunks + 7) / 8);
+    blocks = (int)std::max<i64>(1, std::min<i64>(blocks, max_useful));
+    kp.n_warps = (u64)blocks * 8;
+
+    if (sh.v4) {
+        if (sh.nv == 1) return launch_rows<1, true>(kp, blocks, s);
+        if (sh.nv == 2) return launch_rows<2, true>(kp, blocks, s);
+        return launch_rows<4, true>(kp, blocks, s);
+    }
+    if (sh.nv == 1) return launch_rows<1, false>(kp, blocks, s);
+    if (sh.nv == 2) return launch_rows<2, false>(kp, blocks, s);
+    return launch_rows<4, false>(kp, blocks, s);
+}
+
+}  // namespace
+
+extern "C" int cbm_b200_spmm_update(cbm_b200_plan* p, const float* x, int64_t ldx, float* y,
+                                    int64_t ldy, int32_t f, void* stream) {
+    return run_plan(p, "spmm_update", x, ldx, y, ldy, f, MODE_FUSED, false, (cudaStream_t)stream);
+}
+extern "C" int cbm_b200_fused_spmm_update(cbm_b200_plan* p, const float* x, int64_t ldx, float* y,
+                                          int64_t ldy, int32_t f, void* stream) {
+    return run_plan(p, "fused_spmm_update", x, ldx, y, ldy, f, MODE_FUSED, true,
+                    (cudaStream_t)stream);
+}
+extern "C" int cbm_b200_update(cbm_b200_plan* p, float* y, int64_t ldy, int32_t f, void* stream) {
+    return run_plan(p, "update", nullptr, 0, y, ldy, f, MODE_UPDATE_ONLY, false,
+                    (cudaStream_t)stream);
+}
+extern "C" int cbm_b200_fused_update(cbm_b200_plan* p, float* y, int64_t ldy, int32_t f,
+                                     void* stream) {
+    return run_plan(p, "fused_update", nullptr, 0, y, ldy, f, MODE_UPDATE_ONLY, true,
+                    (cudaStream_t)stream);
+}
+extern "C" int cbm_b200_delta_spmm(cbm_b200_plan* p, const float* x, int64_t ldx, float* y,
+                                   int64_t ldy, int32_t f, void* stream) {
+    return run_plan(p, "delta_spmm", x, ldx, y, ldy, f, MODE_DELTA_ONLY, false,
+                    (cudaStream_t)stream);
+}
+
+extern "C" int cbm_b200_csr_spmm(int32_t n_rows, const int32_t* row_b, const int32_t* row_e,
+                                 const int32_t* col, const float* val, const float* x,
+                                 int64_t ldx, float* y, int64_t ldy, int32_t f, void* stream) {
+    if (n_rows < 0 || (n_rows > 0 && (!row_b || !row_e)))
+        return cbm::fail(CBM_B200_ERR_ARG, "csr_spmm: bad row arrays");
+    int rc = check_dense("csr_spmm", x, ldx, y, ldy, f);
+    if (rc) return rc;
+    if (!x) return cbm::fail(CBM_B200_ERR_ARG, "csr_spmm: x is NULL");
+    if (n_rows == 0) return CBM_B200_OK;
+    const bool can_v4 = (f % 4 == 0) && (ldy % 4 == 0) && (ldx % 4 == 0) && aligned16(y) && aligned16(x);
+    const Shape sh = pick_shape(f, 0, can_v4);
+    const i64 n_units = (i64)sh.n_slabs * n_rows;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess)
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int blocks = (int)std::max<i64>(1, std::min<i64>((i64)sms * 8, (n_units + 7) / 8));
+    cudaStream_t s = (cudaStream_t)stream;
+#define CBM_CSR_LAUNCH(NV, V4)                                                                    \
+    csr_rows_kernel<NV, V4><<<blocks, 256, 0, s>>>(n_rows, row_b, row_e, col, val, x, ldx, y, ldy, \
+                                                   f, sh.slab_w, n_units)
+    if (sh.v4) {
+        if (sh.nv == 1) CBM_CSR_LAUNCH(1, true);
+        else if (sh.nv == 2) CBM_CSR_LAUNCH(2, true);
+        else CBM_CSR_LAUNCH(4, true);
+    } else {
+        if (sh.nv == 1) CBM_CSR_LAUNCH(1, false);
+        else if (sh.nv == 2) CBM_CSR_LAUNCH(2, false);
+        else CBM_CSR_LAUNCH(4, false);
+    }
+#undef CBM_CSR_LAUNCH
+    CBM_CUDA(cudaGetLastError());
+    return CBM_B200_OK;
+}
+
+extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float* y, int32_t f,
+                                         int32_t normalized) {
+    if (!p) return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_host: NULL plan");
+    if (!x || !y || f <= 0) return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_host: bad x / y / f");
+    DeviceGuard g(p->device);
+    // leading dimension rounded up to 4 floats so the 128-bit path applies to any f % 4 == 0
+    const i64 xb = (i64)p->n_labels * f, yb = (i64)p->n_out * f;
+    if (xb > p->stage_x_cap) {
+        cudaFree(p->stage_x);
+        p->stage_x = nullptr;
+        p->stage_x_cap = 0;
+        CBM_CUDA(cudaMalloc((void**)&p->stage_x, (size_t)xb * sizeof(float)));
+        p->stage_x_cap = xb;
+    }
+    if (yb > p->stage_y_cap) {
+        cudaFree(p->stage_y);
+        p->stage_y = nullptr;
+        p->stage_y_cap = 0;
+        CBM_CUDA(cudaMalloc((void**)&p->stage_y, (size_t)std::max<i64>(yb, 1) * sizeof(float)));
+        p->stage_y_cap = yb;
+    }
+    cudaStream_t s = p->own_stream;
+    CBM_CUDA(cudaMemcpyAsync(p->stage_x, x, (size_t)xb * sizeof(float), cudaMemcpyHostToDevice, s));
+    int rc = run_plan(p, "spmm_update_host", p->stage_x, f, p->stage_y, f, f, MODE_FUSED,
+                      normalized != 0, s);
+    if (rc) return rc;
+    CBM_CUDA(cudaMemcpyAsync(y, p->stage_y, (size_t)yb * sizeof(float), cudaMemcpyDeviceToHost, s));
+    return cbm_b200_plan_status(p, s);
+}

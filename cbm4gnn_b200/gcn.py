@@ -1,0 +1,85 @@
+"""GCN layers on the CBM product: ``forward(x, edge_index) = propagate(lin(x))``.
+
+Mirrors gnns/graph_convolutional_network/cbm_gcn.py:10-75: a bias-free linear map with
+Glorot-uniform weights (the reference uses torch_geometric's ``Linear(..., bias=False,
+weight_initializer='glorot')``, restated here on ``torch.nn.Linear`` because torch_geometric is not
+available offline) followed by the normalized CBM propagation.  ``GCNModel`` restates the stacked
+benchmark model of benchmark/parallel/benchmark_gcn_cpu.py:70-89 (ReLU between layers, one CBM
+structure shared by every layer).
+
+The dense map runs through cuBLAS in full fp32 (TF32 is switched off around it) so that results
+stay within the 1e-4 tolerance the reference's tests use.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .message_passing import CBMCudaMessagePassing
+
+
+def _fp32_linear(lin: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    if not x.is_cuda:
+        return lin(x)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        return lin(x)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+class CBMCudaGCN(CBMCudaMessagePassing):
+    def __init__(self, in_channels: int, out_channels: int, alpha: int = 2):
+        super().__init__(normalize=True, alpha=alpha)
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.lin = nn.Linear(in_channels, out_channels, bias=False)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        nn.init.xavier_uniform_(self.lin.weight)  # Glorot-uniform
+
+    def forward(self, x, edge_index):
+        x = _fp32_linear(self.lin, x)
+        return super().forward(edge_index, x=x)
+
+
+# Reference class names (cbm_gcn.py:10, 27, 44, 61).
+class CBMSequentialMKLCSRSparseMatrixGCN(CBMCudaGCN):
+    pass
+
+
+class CBMParallelMKLCSRSparseMatrixGCN(CBMCudaGCN):
+    pass
+
+
+class CBMSequentialTorchCSRSparseMatrixGCN(CBMCudaGCN):
+    pass
+
+
+class CBMParallelTorchCSRSparseMatrixGCN(CBMCudaGCN):
+    pass
+
+
+class GCNModel(nn.Module):
+    """``len(widths) - 1`` GCN layers with ReLU between them, sharing one CBM structure."""
+
+    def __init__(self, widths, structure=None, alpha: int = 2):
+        super().__init__()
+        if len(widths) < 3:
+            raise ValueError("Number of layers must be at least 2")
+        self.layers = nn.ModuleList(CBMCudaGCN(a, b, alpha=alpha) for a, b in zip(widths[:-1], widths[1:]))
+        if structure is not None:
+            self.share(structure)
+
+    def share(self, structure):
+        for layer in self.layers:
+            layer.cached_a_t = structure
+
+    def forward(self, x, edge_index):
+        for i, layer in enumerate(self.layers):
+            if i:
+                x = x.relu()
+            x = layer(x, edge_index)
+        return x

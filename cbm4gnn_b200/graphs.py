@@ -1,0 +1,137 @@
+"""Seeded synthetic graphs standing in for the datasets the reference measures on.
+
+The reference benchmarks on SuiteSparse / Planetoid graphs downloaded at run time
+(benchmark/utility.py:23-42, benchmark/parallel/benchmark_gcn_cpu.py:29-41) and tests on
+Erdős–Rényi graphs from torch_geometric (tests/test_matmul_correctness.py:11-23).  Neither the
+datasets nor torch_geometric are available offline, so the generators below produce graphs with the
+node counts, edge counts and degree shapes the benchmark configurations name.  Every generator
+returns a coalesced, symmetric ``edge_index`` (int64 ``[2, nnz]`` numpy array, rows ascending, no
+self loops) and is a pure function of its arguments.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def _finish(n: int, src: np.ndarray, dst: np.ndarray) -> np.ndarray:
+    """Symmetrise, drop self loops, de-duplicate, sort by (row, col)."""
+    keep = src != dst
+    src, dst = src[keep], dst[keep]
+    a = np.concatenate([src, dst]).astype(np.int64)
+    b = np.concatenate([dst, src]).astype(np.int64)
+    key = np.unique(a * n + b)
+    return np.stack([key // n, key % n])
+
+
+def erdos_renyi(n: int, p: float, seed: int) -> np.ndarray:
+    """Undirected G(n, p) without self loops: the shape of graph the reference's unit tests use
+    (tests/test_matmul_correctness.py:11-23, n=25, p=0.5)."""
+    rng = np.random.default_rng(seed)
+    iu, ju = np.triu_indices(n, k=1)
+    keep = rng.random(iu.shape[0]) < p
+    return _finish(n, iu[keep], ju[keep])
+
+
+def copy_model(n: int, p_copy: float, n_random: int, seed: int, max_degree: int | None = None) -> np.ndarray:
+    """Vertex-copying model: node ``i`` picks a uniform earlier prototype, repeats each of the links
+    the prototype made when it joined with probability ``p_copy`` and adds ``n_random`` links to
+    uniform earlier nodes.  Rows of the (symmetrised) adjacency matrix therefore resemble their
+    prototype's row, which is the similarity CBM compresses; copying makes in-degrees heavy-tailed.
+    ``max_degree`` stops a node from receiving further links once its degree reaches the cap."""
+    rng = np.random.default_rng(seed)
+    links: list[np.ndarray] = [np.empty(0, dtype=np.int64)]
+    deg = np.zeros(n, dtype=np.int64)
+    for i in range(1, n):
+        proto = int(rng.integers(0, i))
+        nb = links[proto]
+        if nb.size:
+            nb = nb[rng.random(nb.size) < p_copy]
+        extra = rng.integers(0, i, size=min(n_random, i))
+        tgt = np.unique(np.concatenate([nb, extra]))
+        if max_degree is not None:
+            tgt = tgt[deg[tgt] < max_degree][:max_degree]
+        deg[tgt] += 1
+        deg[i] += tgt.size
+        links.append(tgt)
+    src = np.repeat(np.arange(n, dtype=np.int64), [l.size for l in links])
+    dst = np.concatenate(links)
+    return _finish(n, src, dst)
+
+
+def stochastic_block_model(n: int, n_communities: int, mu: float, sigma: float, deg_in: float,
+                           deg_out: float, seed: int) -> np.ndarray:
+    """Stochastic block model: community sizes lognormal(mu, sigma) rescaled to sum to ``n``;
+    inside a community each node has ``deg_in`` expected neighbours, across communities ``deg_out``."""
+    rng = np.random.default_rng(seed)
+    raw = rng.lognormal(mu, sigma, n_communities)
+    sizes = np.maximum(2, np.floor(raw * (n / raw.sum()))).astype(np.int64)
+    # settle the rounding remainder on the largest communities
+    diff = int(n - sizes.sum())
+    order = np.argsort(-sizes)
+    k = 0
+    while diff != 0:
+        j = order[k % n_communities]
+        if diff > 0:
+            sizes[j] += 1
+            diff -= 1
+        elif sizes[j] > 2:
+            sizes[j] -= 1
+            diff += 1
+        k += 1
+    starts = np.concatenate([[0], np.cumsum(sizes)[:-1]])
+    label = rng.permutation(n)  # communities are not contiguous in node id
+    src_parts, dst_parts = [], []
+    for s, st in zip(sizes.tolist(), starts.tolist()):
+        pairs = s * (s - 1) // 2
+        p_in = min(1.0, deg_in / max(1, s - 1))
+        m = int(rng.binomial(pairs, p_in))
+        if m == 0:
+            continue
+        a = rng.integers(0, s, size=m)
+        b = rng.integers(0, s, size=m)
+        src_parts.append(label[st + a])
+        dst_parts.append(label[st + b])
+    m_out = int(n * deg_out / 2)
+    src_parts.append(rng.integers(0, n, size=m_out))
+    dst_parts.append(rng.integers(0, n, size=m_out))
+    return _finish(n, np.concatenate(src_parts), np.concatenate(dst_parts))
+
+
+# The five benchmark configurations (graph, operand width, alpha, normalisation, seed).
+CONFIGS = {
+    "c1": dict(kind="copy", n=4096, p_copy=0.8, n_random=3, max_degree=None, f=500, alpha=0,
+               normalized=False, x_dist="uniform01", seed=20241),
+    "c2": dict(kind="copy", n=100_000, p_copy=0.7, n_random=5, max_degree=5000, f=500, alpha=8,
+               normalized=True, x_dist="normal", seed=20242),
+    "c3": dict(kind="sbm", n=235_868, n_communities=2000, mu=4.5, sigma=0.8, deg_in=8.0,
+               deg_out=2.0, f=128, widths=(128, 256, 64), alpha=2, normalized=True,
+               x_dist="normal", seed=20243),
+    "c4": dict(kind="copy", n=132_534, p_copy=0.95, n_random=20, max_degree=None, f=128, alpha=4,
+               normalized=True, x_dist="uniform11", seed=20244),
+    "c5": dict(kind="sbm", n=2_449_029, n_communities=50_000, mu=3.5, sigma=1.0, deg_in=20.0,
+               deg_out=5.0, f=100, widths=(100, 256, 256, 47), alpha=2, normalized=True,
+               x_dist="normal", seed=20245),
+}
+
+
+def make_graph(name: str, scale: float = 1.0) -> np.ndarray:
+    """Edge index of a named configuration; ``scale`` < 1 shrinks the node count (and the number of
+    communities) for quick tests while keeping the degree shape."""
+    c = CONFIGS[name]
+    n = max(16, int(c["n"] * scale))
+    if c["kind"] == "copy":
+        return copy_model(n, c["p_copy"], c["n_random"], c["seed"], c["max_degree"])
+    ncomm = max(2, int(c["n_communities"] * scale))
+    return stochastic_block_model(n, ncomm, c["mu"], c["sigma"], c["deg_in"], c["deg_out"], c["seed"])
+
+
+def make_features(name: str, n: int, f: int | None = None, seed_offset: int = 1000) -> np.ndarray:
+    """Dense operand for a configuration, fp32 ``[n, f]`` with the distribution the configuration names."""
+    c = CONFIGS[name]
+    f = f or c["f"]
+    rng = np.random.default_rng(c["seed"] + seed_offset)
+    if c["x_dist"] == "uniform01":
+        return rng.random((n, f), dtype=np.float32)
+    if c["x_dist"] == "uniform11":
+        return (rng.random((n, f), dtype=np.float32) * 2.0 - 1.0).astype(np.float32)
+    return rng.standard_normal((n, f), dtype=np.float32)

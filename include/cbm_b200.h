@@ -1,0 +1,167 @@
+/*
+ * cbm_b200.h — C ABI of libcbm_b200.so: the compressed-binary-matrix (CBM) product engine for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The library replaces, for the CBM product path only, the pybind11 module `cbm.cbm_mkl_cpp` of
+ * cbm4scale/cbm4gnn (cbm/cbm_extensions.cpp:1757-1771).  Every entry point takes plain pointers
+ * and sizes, returns an `int` status (0 = success) and leaves a message retrievable with
+ * cbm_b200_last_error() on failure.  Nothing here calls exit(); nothing here takes a torch type.
+ *
+ * Conventions shared with the reference: int32 indices, fp32 values, dense operands row-major.
+ * A "tree" is the reference's (mst_row[n+2], mst_col[n]) CSR over n+1 vertices whose last vertex n
+ * is the virtual all-zero root (cbm/cbm_extensions.cpp:274-286); "deltas" is the n x n CSR of
+ * signed differences between each row and its tree parent (cbm/cbm_extensions.cpp:186-261).
+ *
+ * Device pointers are marked [dev], host pointers [host].  `stream` is a cudaStream_t passed as
+ * void* (NULL = the legacy default stream).  Launches are asynchronous on that stream.
+ */
+#ifndef CBM_B200_H
+#define CBM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define CBM_B200_OK 0
+#define CBM_B200_ERR_ARG 1      /* bad argument (null pointer, size, dtype contract, aliasing) */
+#define CBM_B200_ERR_CUDA 2     /* a CUDA runtime call failed */
+#define CBM_B200_ERR_FORMAT 3   /* tree / delta arrays are not a valid CBM structure */
+#define CBM_B200_ERR_TIMEOUT 4  /* a bounded device-side wait ran out (reported by *_status) */
+#define CBM_B200_ERR_ALLOC 5    /* host or device allocation failed */
+
+typedef struct cbm_b200_built cbm_b200_built; /* result of the host builder (host memory only)   */
+typedef struct cbm_b200_plan cbm_b200_plan;   /* device-resident schedule for one GPU            */
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* cbm_b200_last_error(void);
+
+/* Library / build identification: returns e.g. "cbm_b200 0.1 sm_100a". */
+const char* cbm_b200_version(void);
+
+/* --------------------------------------------------------------------------------------------
+ * Host builder.  Replaces cbm_init_v1_ (cbm/cbm_extensions.cpp:8-326, col_mul == NULL) and
+ * cbm_init_v2_ (cbm/cbm_extensions.cpp:328-644, col_mul != NULL), bound in the reference as
+ * from_coo_int32_t_v1_ / from_coo_int32_t_v2_ (cbm/cbm_extensions.cpp:1758-1759).
+ *
+ * Input: a coalesced COO pattern (row[i], col[i]) of an n x n binary matrix [host].  Values are
+ * not needed (the reference passes all-ones only because MKL's syrk wants them).
+ * Candidate rule, virtual edges and weights follow cbm/cbm_extensions.cpp:75-102:
+ *   h(r,c) = |r| + |c| - 2|r ∩ c|;  edge c->r iff h < |r| - alpha;  edge r->c iff h < |c| - alpha;
+ *   edge root->r with weight |r| for every r.
+ * The minimum-cost arborescence rooted at vertex n is computed by the library's own solver (the
+ * reference delegates to the external arbok::TarjanPQ, cbm/cbm_extensions.cpp:109-148).  Ties are
+ * broken deterministically (lowest adjusted weight, then lowest source id), so the same input
+ * always yields byte-identical output.
+ * n_threads <= 0 uses every hardware thread.
+ * ------------------------------------------------------------------------------------------ */
+int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nnz, int32_t n, int32_t alpha,
+                   const float* col_mul, int32_t n_threads, cbm_b200_built** out);
+
+/* Sizes and statistics of a built structure.  Any out-pointer may be NULL.
+ *   n_delta       number of delta entries (= total weight of the arborescence)
+ *   n_candidates  number of candidate edges offered to the solver, virtual edges included
+ *   n_root_children, depth   shape of the tree (depth of a root child = 1)
+ *   seconds[4]    wall time of: CSR + candidate graph, arborescence, delta emission, total */
+int cbm_b200_built_info(const cbm_b200_built* b, int64_t* n_delta, int64_t* n_candidates,
+                        int32_t* n_root_children, int32_t* depth, double* seconds);
+
+/* Copy the structure out [host].  mst_row has n+2 entries, mst_col n (children sorted by id).
+ * delta_crow has n+1 entries; delta_col / delta_val have n_delta, columns ascending inside a row:
+ * the CSR the reference obtains by coalescing its COO output (cbm/cbm.py:120-141).  parent (n
+ * entries, the virtual root written as n) may be NULL. */
+int cbm_b200_built_export_csr(const cbm_b200_built* b, int32_t* mst_row, int32_t* mst_col,
+                              int32_t* delta_crow, int32_t* delta_col, float* delta_val,
+                              int32_t* parent);
+
+/* The same deltas in the reference's native output layout: COO triples in breadth-first order of
+ * the tree (cbm/cbm_extensions.cpp:166-270, 288-325).  Each array has n_delta entries. */
+int cbm_b200_built_export_coo(const cbm_b200_built* b, int32_t* delta_row, int32_t* delta_col,
+                              float* delta_val);
+
+void cbm_b200_built_free(cbm_b200_built* b);
+
+/* --------------------------------------------------------------------------------------------
+ * Plans.  A plan is the device-side schedule derived from the reference-format arrays; the arrays
+ * themselves are consumed unmodified.  It plays the role of the MKL handle the reference re-creates
+ * on every call (cbm/cbm_extensions.cpp:679, 1134, 1252) plus the DFS stack of its tree walk.
+ *
+ * All array arguments are [host].  `multiplier` (n floats, D^-1/2) may be NULL for the
+ * unnormalized product.  Sharding: `perm` (n entries, NULL = identity) relabels vertices with
+ * distinct labels in [0, n_labels), n_labels >= n (n_labels = 0 means n; labels that no vertex
+ * carries are padding that lets every shard have the same number of rows).  The plan computes only
+ * rows whose label lies in [own_begin, own_end); those rows must form whole subtrees of the
+ * virtual root.  In every product call the dense right-hand side is indexed by LABEL (n_labels
+ * rows), and the output pointer addresses the shard: output row (label - own_begin); padding rows
+ * of the output are never written.  own_begin = 0, own_end = n_labels computes everything.
+ * `device` is the CUDA device ordinal that owns the plan.
+ * ------------------------------------------------------------------------------------------ */
+int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int32_t* mst_col,
+                         const int32_t* delta_crow, const int32_t* delta_col,
+                         const float* delta_val, const float* multiplier, const int32_t* perm,
+                         int32_t n_labels, int32_t own_begin, int32_t own_end, int32_t device,
+                         cbm_b200_plan** out);
+
+void cbm_b200_plan_destroy(cbm_b200_plan* p);
+
+/* Figures used by the byte model: rows computed by this plan, delta entries of those rows, rows
+ * whose parent is the virtual root, tree depth, and device bytes held by the plan. */
+int cbm_b200_plan_info(const cbm_b200_plan* p, int32_t* n_rows, int64_t* n_delta,
+                       int32_t* n_root_children, int32_t* depth, int64_t* device_bytes);
+
+/* Tuning knobs (0 keeps the default): column-slab width in floats, thread blocks per launch. */
+int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t n_blocks);
+
+/* Waits for `stream`, then reports whether any launch since the last call gave up on a bounded
+ * wait (CBM_B200_ERR_TIMEOUT) — in that case the outputs of that launch are invalid. */
+int cbm_b200_plan_status(cbm_b200_plan* p, void* stream);
+
+/* --------------------------------------------------------------------------------------------
+ * Products.  x [dev]: n_labels x f floats with leading dimension ldx; y [dev]:
+ * (own_end-own_begin) x f with leading dimension ldy; x and y must not overlap.
+ *
+ * cbm_b200_spmm_update        y = A x: delta product fused with the tree update y_v += y_parent.
+ *                             Replaces seq_/omp_s_spmm_update_csr_int32
+ *                             (cbm/cbm_extensions.cpp:650-740, 1108-1219).
+ * cbm_b200_fused_spmm_update  y = D^-1/2 A D^-1/2 x for a plan created with `multiplier`:
+ *                             y_r *= s_r for root children, y_v = (y_v + y_u / s_u) s_v below.
+ *                             Replaces seq_/omp_s_fused_spmm_update_csr_int32
+ *                             (cbm/cbm_extensions.cpp:845-996, 1224-1374).
+ * cbm_b200_update             in-place tree update of y that already holds the delta product.
+ *                             Replaces seq_/omp_s_update_csr_int32 and omp_s_update_avx_int32
+ *                             (cbm/cbm_extensions.cpp:742-786, 1485-1610, 1612-1705).
+ * cbm_b200_fused_update       normalized in-place update.  Replaces seq_/omp_s_fused_update_csr_int32
+ *                             (cbm/cbm_extensions.cpp:998-1105, 1376-1483).
+ * cbm_b200_delta_spmm         y = deltas x from the plan's resident copy of the delta CSR (the
+ *                             `self.deltas @ x` step of cbm/cbm.py:255-275).
+ * ------------------------------------------------------------------------------------------ */
+int cbm_b200_spmm_update(cbm_b200_plan* p, const float* x, int64_t ldx, float* y, int64_t ldy,
+                         int32_t f, void* stream);
+int cbm_b200_fused_spmm_update(cbm_b200_plan* p, const float* x, int64_t ldx, float* y,
+                               int64_t ldy, int32_t f, void* stream);
+int cbm_b200_update(cbm_b200_plan* p, float* y, int64_t ldy, int32_t f, void* stream);
+int cbm_b200_fused_update(cbm_b200_plan* p, float* y, int64_t ldy, int32_t f, void* stream);
+int cbm_b200_delta_spmm(cbm_b200_plan* p, const float* x, int64_t ldx, float* y, int64_t ldy,
+                        int32_t f, void* stream);
+
+/* Plain CSR product y = M x for any fp32 CSR with device-resident arrays [dev].  Replaces
+ * seq_/omp_s_spmm_csr_int32 (cbm/cbm_extensions.cpp:790-843, 1707-1755).  row_b / row_e are the
+ * reference's 4-array form (row_b = crow[:-1], row_e = crow[1:]). */
+int cbm_b200_csr_spmm(int32_t n_rows, const int32_t* row_b, const int32_t* row_e,
+                      const int32_t* col, const float* val, const float* x, int64_t ldx, float* y,
+                      int64_t ldy, int32_t f, void* stream);
+
+/* Host-buffer forms of the two fused products: x [host] n_labels x f and y [host]
+ * (own_end-own_begin) x f, both contiguous (ld = f).  The call copies x to the device, runs the product and copies y back on the
+ * plan's own stream, and returns when y is complete.  Staging buffers belong to the plan and grow
+ * on demand.  `normalized` != 0 selects cbm_b200_fused_spmm_update.  These are what a caller
+ * holding CPU tensors, as every caller of the reference does, binds to. */
+int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float* y, int32_t f,
+                              int32_t normalized);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CBM_B200_H */

@@ -1,0 +1,149 @@
+"""Host builder of the product (libcbm_b200.so) against the restated builder and its invariants."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from cbm4gnn_b200 import _lib, graphs
+from cbm4gnn_b200.cbm import cbm_matrix
+from oracle import cbm_oracle as orc
+from helpers import with_self_loops
+
+
+def _cbm(ei, alpha=0, normalized=False):
+    e = torch.from_numpy(ei).to(torch.int32)
+    return cbm_matrix(e, torch.ones(e.shape[1]), alpha=alpha, normalized=normalized)
+
+
+@pytest.mark.parametrize("alpha", [1, 2, 3, 4])   # the values tests/test_cbm_creation.py:31-39 sweeps
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_structure_valid_and_optimal(seed, alpha):
+    ei = graphs.erdos_renyi(25, 0.5, seed)
+    c = _cbm(ei, alpha)
+    assert c is not None
+    c.check_format(torch.from_numpy(ei))
+    ref = orc.build_structure(ei, alpha)
+    # the optimum weight is unique even where the optimal tree is not
+    assert c.build_info["n_delta"] == ref["weight"]
+    assert c.mst_row.dtype == torch.int32 and c.mst_col.dtype == torch.int32
+    assert c.mst_row.numel() == c.num_rows + 2 and c.mst_col.numel() == c.num_rows
+    assert c.deltas.layout == torch.sparse_csr and tuple(c.deltas.shape) == (c.num_rows, c.num_rows)
+    assert c.deltas.values().dtype == torch.float32
+
+
+def test_structure_optimal_against_networkx():
+    nx = pytest.importorskip("networkx")
+    ei = graphs.make_graph("c1", scale=0.03)
+    n = int(ei.max()) + 1
+    c = _cbm(ei, 0)
+    g = nx.DiGraph()
+    for u, v, w in orc.candidate_edges(ei, n, 0):
+        if not g.has_edge(u, v) or g[u][v]["weight"] > w:
+            g.add_edge(u, v, weight=w)
+    ref = nx.minimum_spanning_arborescence(g)
+    assert c.build_info["n_delta"] == sum(d["weight"] for _, _, d in ref.edges(data=True))
+
+
+def test_candidate_rule_respected():
+    """Every tree edge u -> v below the virtual root satisfies h(u, v) < |v| - alpha
+    (cbm/cbm_extensions.cpp:93-101) and carries exactly h(u, v) delta entries."""
+    alpha = 2
+    ei = graphs.make_graph("c1", scale=0.2)
+    c = _cbm(ei, alpha)
+    n = c.num_rows
+    rows = orc.pattern_rows(ei, n)
+    dl = np.diff(c._crow)
+    for v in range(n):
+        u = int(c._parent[v])
+        if u == n:
+            assert dl[v] == rows[v].size
+        else:
+            h = np.setxor1d(rows[u], rows[v]).size
+            assert h < rows[v].size - alpha and dl[v] == h
+
+
+def test_deterministic_and_thread_independent():
+    ei = graphs.make_graph("c1", scale=0.25)
+    e = torch.from_numpy(ei).to(torch.int32)
+    a = cbm_matrix(e, torch.ones(e.shape[1]), alpha=1, n_threads=1)
+    b = cbm_matrix(e, torch.ones(e.shape[1]), alpha=1, n_threads=4)
+    for x, y in ((a.mst_row, b.mst_row), (a.mst_col, b.mst_col)):
+        assert torch.equal(x, y)
+    assert np.array_equal(a._crow, b._crow) and np.array_equal(a._dcol, b._dcol)
+    assert np.array_equal(a._dval, b._dval)
+
+
+def test_normalized_values_are_signed_multipliers():
+    ei = with_self_loops(graphs.erdos_renyi(30, 0.3, 5))
+    c = _cbm(ei, 2, normalized=True)
+    c.check_format(torch.from_numpy(ei))
+    mult = c.col_multiplier.numpy()
+    np.testing.assert_array_equal(mult, orc.row_multiplier(ei, c.num_rows))
+    np.testing.assert_array_equal(np.abs(c._dval), mult[c._dcol])
+
+
+def test_coo_export_is_breadth_first_and_equivalent():
+    ei = graphs.erdos_renyi(25, 0.5, 11)
+    row, col = ei[0].astype(np.int32), ei[1].astype(np.int32)
+    n = int(ei.max()) + 1
+    L = _lib.lib()
+    h = ctypes.c_void_p(0)
+    p = lambda a: ctypes.c_void_p(a.ctypes.data)
+    _lib.check(L.cbm_b200_build(p(row), p(col), row.shape[0], n, 2, None, 0, ctypes.byref(h)))
+    nd = ctypes.c_int64()
+    _lib.check(L.cbm_b200_built_info(h, ctypes.byref(nd), None, None, None, None))
+    mst_row, mst_col = np.empty(n + 2, np.int32), np.empty(n, np.int32)
+    crow, dcol, dval = np.empty(n + 1, np.int32), np.empty(nd.value, np.int32), np.empty(nd.value, np.float32)
+    _lib.check(L.cbm_b200_built_export_csr(h, p(mst_row), p(mst_col), p(crow), p(dcol), p(dval), None))
+    cr, cc, cv = np.empty(nd.value, np.int32), np.empty(nd.value, np.int32), np.empty(nd.value, np.float32)
+    _lib.check(L.cbm_b200_built_export_coo(h, p(cr), p(cc), p(cv)))
+    L.cbm_b200_built_free(h)
+    # the reference coalesces its COO output into CSR (cbm/cbm.py:120-141): same matrix
+    o = np.lexsort((cc, cr))
+    assert np.array_equal(cc[o], dcol) and np.array_equal(cv[o], dval)
+    assert np.array_equal(np.bincount(cr, minlength=n), np.diff(crow))
+    # rows appear in breadth-first order of the tree
+    first = [r for i, r in enumerate(cr.tolist()) if i == 0 or cr[i - 1] != r]
+    bfs = []
+    frontier = [n]
+    while frontier:
+        nxt = []
+        for u in frontier:
+            nxt.extend(mst_col[mst_row[u]:mst_row[u + 1]].tolist())
+        bfs.extend(nxt)
+        frontier = nxt
+    # the walk is a queue, not level-synchronous, but children stay in mst_col order: same sequence
+    assert first == [v for v in bfs if crow[v + 1] > crow[v]]
+
+
+def test_edge_cases():
+    # a row without entries (node 2 has only an incoming edge) and duplicate input entries
+    ei = np.array([[0, 0, 1, 1, 3, 3, 0], [1, 2, 0, 2, 0, 1, 1]], dtype=np.int64)
+    c = _cbm(ei, 0)
+    c.check_format(torch.from_numpy(ei))
+    assert c.num_rows == 4 and c.build_info["n_delta"] <= 6
+    # single entry
+    c1 = _cbm(np.array([[0], [0]]), 0)
+    assert c1.num_rows == 1 and c1.build_info["n_delta"] == 1
+    # identical rows compress to nothing below the first
+    ei = np.array([[0, 0, 1, 1, 2, 2], [3, 4, 3, 4, 3, 4]], dtype=np.int64)
+    c2 = _cbm(ei, 0)
+    assert c2.build_info["n_delta"] == 2
+    c2.check_format(torch.from_numpy(ei))
+    # large alpha forbids every non-virtual edge
+    c3 = _cbm(graphs.erdos_renyi(25, 0.5, 3), alpha=1000)
+    assert c3.build_info["n_root_children"] == c3.num_rows and c3.build_info["depth"] == 1
+
+
+def test_builder_rejects_bad_input():
+    L = _lib.lib()
+    h = ctypes.c_void_p(0)
+    row = np.array([0, 5], dtype=np.int32)
+    col = np.array([1, 0], dtype=np.int32)
+    p = lambda a: ctypes.c_void_p(a.ctypes.data)
+    assert L.cbm_b200_build(p(row), p(col), 2, 3, 0, None, 0, ctypes.byref(h)) == 1
+    assert b"out of range" in L.cbm_b200_last_error()
+    assert L.cbm_b200_build(None, None, 2, 3, 0, None, 0, ctypes.byref(h)) == 1
+    with pytest.raises(ValueError):
+        cbm_matrix(torch.zeros((3, 4), dtype=torch.int32), torch.ones(4))

@@ -1,0 +1,300 @@
+"""Parity of the CUDA products with the CPU restatement, the fixtures and dense / sparse A @ X.
+
+Every product here goes through the C ABI of libcbm_b200.so (``cbm_matrix`` methods are thin ctypes
+calls).  Tolerance for floating-point inputs: atol = rtol = 1e-4 (fp32), the reference's own figure
+(tests/test_matmul_correctness.py:43); integer-valued inputs must match bit for bit.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from cbm4gnn_b200 import _lib, graphs
+from cbm4gnn_b200.cbm import cbm_matrix, _Plan
+from oracle import cbm_oracle as orc
+from conftest import golden_case
+from helpers import dense_product, sparse_product, with_self_loops
+
+pytestmark = pytest.mark.gpu
+TOL = dict(atol=1e-4, rtol=1e-4)
+
+
+def _cbm(ei, alpha=0, normalized=False):
+    e = torch.from_numpy(np.ascontiguousarray(ei)).to(torch.int32)
+    return cbm_matrix(e, torch.ones(e.shape[1]), alpha=alpha, normalized=normalized)
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _oracle(c, x, parallel=True):
+    mr, mc = c.mst_row.numpy(), c.mst_col.numpy()
+    if c.normalized:
+        return orc.fused_spmm_update(mr, mc, c._crow, c._dcol, c._dval, c.col_multiplier.numpy(), x, parallel)
+    return orc.spmm_update(mr, mc, c._crow, c._dcol, c._dval, x, parallel)
+
+
+@pytest.mark.parametrize("k", range(5))
+@pytest.mark.parametrize("alpha", [0, 2, 3])
+def test_golden_unnormalized_bit_exact(golden, k, alpha):
+    ei, x, y, _ = golden_case(golden, k)
+    c = _cbm(ei, alpha)
+    xd = _dev(x)
+    out = torch.full_like(xd, float("nan"))
+    c.omp_mkl_csr_spmm_update(xd, out)
+    np.testing.assert_array_equal(out.cpu().numpy(), y)
+    out2 = torch.full_like(xd, float("nan"))
+    c.seq_mkl_csr_spmm_update(xd, out2)
+    assert torch.equal(out, out2)
+    # two-step form of cbm/cbm.py:255-265
+    np.testing.assert_array_equal(c.seq_torch_csr_matmul(xd).cpu().numpy(), y)
+    np.testing.assert_array_equal(c.omp_torch_csr_matmul(xd).cpu().numpy(), y)
+    c.plan().status()
+
+
+@pytest.mark.parametrize("k", range(5))
+def test_golden_normalized(golden, k):
+    ei, x, _, y_norm = golden_case(golden, k)
+    c = _cbm(with_self_loops(ei), 2, normalized=True)
+    xd = _dev(x)
+    out = torch.empty_like(xd)
+    c.omp_mkl_csr_fused_spmm_update(xd, out)
+    np.testing.assert_allclose(out.cpu().numpy(), y_norm, **TOL)
+    np.testing.assert_allclose(c.omp_torch_csr_fused_matmul(xd).cpu().numpy(), y_norm, **TOL)
+    np.testing.assert_allclose(out.cpu().numpy(), _oracle(c, x), **TOL)
+
+
+def test_host_tensors_are_staged_through_the_gpu(golden):
+    ei, x, y, y_norm = golden_case(golden, 0)
+    c = _cbm(ei, 2)
+    out = torch.empty((c.num_rows, x.shape[1]))
+    c.omp_mkl_csr_spmm_update(torch.from_numpy(x), out)
+    np.testing.assert_array_equal(out.numpy(), y)
+    np.testing.assert_array_equal(c.seq_torch_csr_matmul(torch.from_numpy(x)).numpy(), y)
+    cn = _cbm(with_self_loops(ei), 2, normalized=True)
+    outn = torch.empty((c.num_rows, x.shape[1]))
+    cn.seq_mkl_csr_fused_spmm_update(torch.from_numpy(x), outn)
+    np.testing.assert_allclose(outn.numpy(), y_norm, **TOL)
+
+
+@pytest.fixture(scope="module")
+def c1():
+    ei = graphs.make_graph("c1")
+    return ei, _cbm(ei, 0)
+
+
+def test_config1_full(c1):
+    """N = 4096 copy-model graph, alpha = 0, unnormalized, F = 500, X uniform[0,1): against dense
+    A @ X and against both CPU paths of the restatement."""
+    ei, c = c1
+    n = c.num_rows
+    x = graphs.make_features("c1", n)
+    out = torch.empty((n, 500), device="cuda")
+    c.omp_mkl_csr_spmm_update(_dev(x), out)
+    got = out.cpu().numpy()
+    np.testing.assert_allclose(got, dense_product(ei, x, False), **TOL)
+    np.testing.assert_allclose(got, _oracle(c, x, parallel=False), **TOL)
+    np.testing.assert_allclose(got, _oracle(c, x, parallel=True), **TOL)
+    c.plan().status()
+
+
+@pytest.mark.parametrize("f", [1, 3, 4, 31, 47, 64, 100, 128, 132, 250, 256, 500, 516, 1024, 1100])
+def test_operand_widths(c1, f):
+    ei, c = c1
+    n = c.num_rows
+    rng = np.random.default_rng(f)
+    x = rng.integers(-4, 5, size=(n, f)).astype(np.float32)  # exact in fp32
+    want = sparse_product(ei, x, False).astype(np.float32)
+    out = torch.empty((n, f), device="cuda")
+    c.omp_mkl_csr_spmm_update(_dev(x), out)
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    d = torch.empty((n, f), device="cuda")
+    c.omp_mkl_csr_spmm(_dev(x), d)
+    np.testing.assert_array_equal(d.cpu().numpy(), orc.csr_spmm(c._crow, c._dcol, c._dval, x))
+    c.omp_mkl_csr_update(d)
+    np.testing.assert_array_equal(d.cpu().numpy(), want)
+
+
+def test_strided_operands(c1):
+    ei, c = c1
+    n = c.num_rows
+    rng = np.random.default_rng(1)
+    for f, ld in ((64, 80), (30, 33), (128, 500)):
+        xb = torch.zeros((n, ld), device="cuda")
+        yb = torch.full((n, ld), -7.0, device="cuda")
+        x = rng.integers(-4, 5, size=(n, f)).astype(np.float32)
+        xb[:, :f] = _dev(x)
+        c.omp_mkl_csr_spmm_update(xb[:, :f], yb[:, :f])
+        np.testing.assert_array_equal(yb[:, :f].cpu().numpy(), sparse_product(ei, x, False).astype(np.float32))
+        assert torch.all(yb[:, f:] == -7.0)  # nothing outside the view is touched
+
+
+def test_config2_scaled_normalized():
+    """Copy model p = 0.7, 5 random links, alpha = 8, D^-1/2 (A+I) D^-1/2, X ~ N(0,1)."""
+    ei = with_self_loops(graphs.make_graph("c2", scale=0.1))
+    c = _cbm(ei, 8, normalized=True)
+    n = c.num_rows
+    x = graphs.make_features("c2", n, f=500)
+    out = torch.empty((n, 500), device="cuda")
+    c.omp_mkl_csr_fused_spmm_update(_dev(x), out)
+    got = out.cpu().numpy()
+    np.testing.assert_allclose(got, sparse_product(ei, x, True), **TOL)
+    np.testing.assert_allclose(got, _oracle(c, x), **TOL)
+    # the weights of the plain-CSR comparison matrix (gnns/utility.py:25-33) give the same product
+    from cbm4gnn_b200.utility import normalize_edge_index
+    w = normalize_edge_index(torch.from_numpy(ei)).cuda()
+    a = torch.sparse_coo_tensor(torch.from_numpy(ei).cuda(), w, (n, n)).to_sparse_csr()
+    np.testing.assert_allclose(got, (a @ _dev(x)).cpu().numpy(), **TOL)
+    # update-only form on the delta product
+    d = torch.empty_like(out)
+    c.seq_mkl_csr_spmm(_dev(x), d)
+    c.seq_mkl_csr_fused_update(d)
+    np.testing.assert_allclose(d.cpu().numpy(), got, **TOL)
+
+
+def test_alpha_sweep_high_similarity():
+    """Small stand-in for the high-similarity configuration: alpha in {0, 4, 16, 64}."""
+    ei = with_self_loops(graphs.copy_model(3000, 0.95, 20, 77))
+    n = int(ei.max()) + 1
+    x = (np.random.default_rng(5).random((n, 128), dtype=np.float32) * 2 - 1).astype(np.float32)
+    want = sparse_product(ei, x, True)
+    prev = None
+    for alpha in (0, 4, 16, 64):
+        c = _cbm(ei, alpha, normalized=True)
+        out = torch.empty((n, 128), device="cuda")
+        c.omp_mkl_csr_fused_spmm_update(_dev(x), out)
+        np.testing.assert_allclose(out.cpu().numpy(), want, **TOL)
+        if prev is not None:
+            assert c.build_info["n_delta"] >= prev  # a larger alpha never compresses more
+        prev = c.build_info["n_delta"]
+
+
+def test_deep_chain_and_repeated_calls():
+    """Nested rows r_i = {0..i} give a tree that is one chain of depth n: every row waits for the
+    row before it.  Also exercises repeated launches on one plan and changing widths."""
+    n = 1500
+    rows = np.repeat(np.arange(n), np.arange(1, n + 1))
+    cols = np.concatenate([np.arange(i + 1) for i in range(n)])
+    ei = np.stack([rows, cols])
+    c = _cbm(ei, 0)
+    assert c.build_info["depth"] == n and c.build_info["n_delta"] == n
+    for f in (8, 128, 500, 8):
+        x = np.random.default_rng(f).integers(-3, 4, size=(n, f)).astype(np.float32)
+        want = np.cumsum(x.astype(np.float64), axis=0).astype(np.float32)
+        for _ in range(3):
+            out = torch.empty((n, f), device="cuda")
+            c.omp_mkl_csr_spmm_update(_dev(x), out)
+            np.testing.assert_array_equal(out.cpu().numpy(), want)
+    c.plan().status()
+
+
+def test_csr_spmm_any_matrix():
+    """Plain CSR product with arbitrary fp32 values (the MKL CSR baseline of the reference,
+    cbm/cbm_extensions.cpp:1707-1755), 4-array form, device pointers."""
+    rng = np.random.default_rng(9)
+    ei = graphs.make_graph("c1", scale=0.5)
+    n = int(ei.max()) + 1
+    import scipy.sparse as sp
+    val = rng.standard_normal(ei.shape[1]).astype(np.float32)
+    a = sp.csr_matrix((val, (ei[0], ei[1])), shape=(n, n))
+    crow, col = a.indptr.astype(np.int32), a.indices.astype(np.int32)
+    L = _lib.lib()
+    for f in (47, 128, 500):
+        x = rng.standard_normal((n, f)).astype(np.float32)
+        y = torch.empty((n, f), device="cuda")
+        rb, re_, cd, vd, xd = _dev(crow[:-1]), _dev(crow[1:]), _dev(col), _dev(a.data), _dev(x)
+        _lib.check(L.cbm_b200_csr_spmm(n, rb.data_ptr(), re_.data_ptr(), cd.data_ptr(), vd.data_ptr(),
+                                       xd.data_ptr(), f, y.data_ptr(), f, f,
+                                       torch.cuda.current_stream().cuda_stream))
+        np.testing.assert_allclose(y.cpu().numpy(), orc.csr_spmm(crow, col, a.data, x), **TOL)
+
+
+def test_sharded_plans_cover_the_product():
+    """Two plans, each owning whole subtrees of the virtual root under a relabelling, together
+    reproduce the full product (the unit of the multi-GPU split)."""
+    from cbm4gnn_b200.sharding import partition_subtrees
+    ei = with_self_loops(graphs.make_graph("c1"))
+    c = _cbm(ei, 0, normalized=True)
+    n = c.num_rows
+    part = partition_subtrees(c, 2)
+    x = graphs.make_features("c1", n, f=64)
+    want = sparse_product(ei, x, True)
+    xp = np.zeros((part.n_labels, 64), dtype=np.float32)
+    xp[part.perm] = x            # the operand is indexed by label
+    xd = _dev(xp)
+    y_full = torch.zeros((part.n_labels, 64), device="cuda")
+    for g in range(2):
+        b, e = part.offsets(g)
+        plan = _Plan(n, c.mst_row.numpy(), c.mst_col.numpy(), c._crow, c._dcol, c._dval,
+                     c.col_multiplier.numpy(), 0, perm=part.perm, n_labels=part.n_labels, own_begin=b,
+                     own_end=e)
+        assert plan.n_rows == part.counts[g]
+        y = y_full[b:e]
+        _lib.check(_lib.lib().cbm_b200_fused_spmm_update(plan.handle, xd.data_ptr(), 64, y.data_ptr(), 64, 64,
+                                                         torch.cuda.current_stream().cuda_stream))
+        plan.status()
+    np.testing.assert_allclose(y_full.cpu().numpy()[part.perm], want, **TOL)
+    # an owned range that cuts a subtree is refused
+    with pytest.raises(RuntimeError, match="cuts a subtree|owned"):
+        ident = np.arange(n, dtype=np.int32)
+        deep = int(np.nonzero(c._parent != n)[0][0])
+        _Plan(n, c.mst_row.numpy(), c.mst_col.numpy(), c._crow, c._dcol, c._dval, c.col_multiplier.numpy(), 0,
+              perm=ident, n_labels=n, own_begin=deep, own_end=deep + 1)
+
+
+def test_argument_errors(c1):
+    _, c = c1
+    n = c.num_rows
+    x = torch.ones((n, 8), device="cuda")
+    with pytest.raises(RuntimeError, match="kFloat32"):
+        c.omp_mkl_csr_spmm_update(x.double(), torch.empty((n, 8), device="cuda"))
+    with pytest.raises(RuntimeError, match="shape"):
+        c.omp_mkl_csr_spmm_update(x, torch.empty((n, 9), device="cuda"))
+    with pytest.raises(RuntimeError, match="col_multiplier"):
+        c.omp_mkl_csr_fused_spmm_update(x, torch.empty_like(x))
+    with pytest.raises(RuntimeError, match="alias"):
+        c.omp_mkl_csr_spmm_update(x, x)
+    p = c.plan()
+    bad = ctypes.c_void_p(0)
+    assert _lib.lib().cbm_b200_plan_create(n, c.mst_row.numpy().ctypes.data, c.mst_col.numpy().ctypes.data,
+                                           c._crow.ctypes.data, c._dcol.ctypes.data, c._dval.ctypes.data, None,
+                                           None, 0, 0, n, 99, ctypes.byref(bad)) != 0
+    # a tree with a cycle is refused
+    mr = c.mst_row.numpy().copy()
+    mc = c.mst_col.numpy().copy()
+    mc[0] = mc[1]
+    assert _lib.lib().cbm_b200_plan_create(n, mr.ctypes.data, mc.ctypes.data, c._crow.ctypes.data,
+                                           c._dcol.ctypes.data, c._dval.ctypes.data, None, None, 0, 0, n, 0,
+                                           ctypes.byref(bad)) == 3
+    p.status()
+
+
+@pytest.fixture(scope="module")
+def c2_full():
+    ei = with_self_loops(graphs.make_graph("c2"))
+    return ei, _cbm(ei, 8, normalized=True)
+
+
+def test_config2_full_size_properties(c2_full):
+    """At the benchmark's full size (N = 100 000, F = 500) the CPU restatement is too slow for a
+    unit test, so parity is checked on a row sample against float64 CSR and through linearity:
+    A(2x - 3z) == 2 A x - 3 A z."""
+    ei, c = c2_full
+    n = c.num_rows
+    x = graphs.make_features("c2", n)
+    z = graphs.make_features("c2", n, seed_offset=2000)
+    xd, zd = _dev(x), _dev(z)
+    yx, yz, yc = (torch.empty((n, 500), device="cuda") for _ in range(3))
+    c.omp_mkl_csr_fused_spmm_update(xd, yx)
+    c.omp_mkl_csr_fused_spmm_update(zd, yz)
+    c.omp_mkl_csr_fused_spmm_update(2 * xd - 3 * zd, yc)
+    torch.testing.assert_close(yc, 2 * yx - 3 * yz, atol=1e-3, rtol=1e-4)
+    rows = np.random.default_rng(0).choice(n, 2000, replace=False)
+    import scipy.sparse as sp
+    a = sp.csr_matrix((np.ones(ei.shape[1]), (ei[0], ei[1])), shape=(n, n))
+    s = np.asarray(a.sum(1)).ravel() ** -0.5
+    want = (sp.diags(s[rows]) @ a[rows] @ sp.diags(s)) @ x.astype(np.float64)
+    np.testing.assert_allclose(yx[torch.from_numpy(rows).cuda()].cpu().numpy(), want, **TOL)
+    c.plan().status()

@@ -53,16 +53,20 @@ using u64 = unsigned long long;
                                                     cudaGetErrorString(e__));               \
     } while (0)
 
-// One row of the schedule, in processing order.  32 bytes, read as two 16-byte loads.
+// One work item of the schedule, in processing order.  32 bytes, read as two 16-byte loads.
+// A row with many delta entries is cut into segments: all but the last become PARTIAL items that
+// leave their share of the gather in a scratch slot; the last item of the row (placed directly
+// after them) adds those slots to its own share and finishes the row.
 struct __align__(16) RowDesc {
-    i32 out_row;      // row of y this item produces (local to the shard)
+    i32 out_row;      // row of y this item produces (local to the shard); scratch slot if PARTIAL
     i32 parent_row;   // row of y holding the parent's finished row, -1 under the virtual root
     i32 parent_pos;   // parent's position in processing order (index of its ready flag)
-    i32 has_children; // non-zero: someone will wait for this row
-    i32 beg, end;     // delta entries of the row in the plan's col/val arrays
+    i32 flags;        // UNIT_* bits; bits 8.. = number of PARTIAL items directly before this one
+    i32 beg, end;     // delta entries of the item in the plan's col/val arrays
     float scale;      // s_v  = D^-1/2 of this row (1 when the plan has no multiplier)
     float inv_parent; // 1/s_u of the parent (1 when none)
 };
+enum : int { UNIT_PUBLISH = 1, UNIT_PARTIAL = 2, UNIT_NPART_SHIFT = 8 };
 
 enum Mode : int { MODE_FUSED = 0, MODE_DELTA_ONLY = 1, MODE_UPDATE_ONLY = 2 };
 
@@ -75,13 +79,13 @@ struct KParams {
     i64 ldx, ldy;
     i32 f;
     i32 slab_w;     // columns per slab
-    i32 n_rows;     // rows computed by this plan
-    i64 n_units;    // n_rows * n_slabs
-    i32 chunk;      // units claimed per counter increment
-    u64 n_chunks;
+    i32 n_items;    // work items per slab (rows + extra segments of long rows)
+    i64 n_units;    // n_items * n_slabs
+    float* scratch; // n_slabs * n_slots * slab_w floats: partial sums of long rows
+    i32 n_slots;
     u64* counter;   // [0] next chunk to claim, [1] warps that have left; both 0 between launches
     u64 n_warps;    // warps in this launch
-    i32* flags;     // n_slabs * n_rows ready flags holding the epoch of the launch that set them
+    i32* flags;     // n_slabs * n_items ready flags holding the epoch of the launch that set them
     i32 epoch;
     i32* status;    // 0 ok; non-zero: a wait gave up
     i32 mode;
@@ -135,6 +139,19 @@ struct Vec<true> {
     static constexpr int E = 4;
     static __device__ __forceinline__ T zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
     static __device__ __forceinline__ T ld_ro(const float* p) { return __ldg((const float4*)p); }
+    // Read-only fetch that is skipped (giving zeros) when `on` is false.  Written as volatile asm
+    // so that a batch of fetches stays a batch: the compiler may not sink one below its use.
+    static __device__ __forceinline__ T ld_ro_if(const float* p, bool on) {
+        T v;
+        asm volatile(
+            "{\n\t.reg .pred q;\n\tsetp.ne.s32 q, %5, 0;\n\t"
+            "mov.f32 %0, 0f00000000;\n\tmov.f32 %1, 0f00000000;\n\t"
+            "mov.f32 %2, 0f00000000;\n\tmov.f32 %3, 0f00000000;\n\t"
+            "@q ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];\n\t}"
+            : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+            : "l"(p), "r"((int)on));
+        return v;
+    }
     static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg((const float4*)p); }
     static __device__ __forceinline__ void st(float* p, T v) { *(float4*)p = v; }
     static __device__ __forceinline__ T fma(float w, T a, T c) {
@@ -158,14 +175,38 @@ struct Vec<false> {
     static constexpr int E = 1;
     static __device__ __forceinline__ T zero() { return 0.f; }
     static __device__ __forceinline__ T ld_ro(const float* p) { return __ldg(p); }
+    static __device__ __forceinline__ T ld_ro_if(const float* p, bool on) {
+        T v;
+        asm volatile(
+            "{\n\t.reg .pred q;\n\tsetp.ne.s32 q, %2, 0;\n\tmov.f32 %0, 0f00000000;\n\t"
+            "@q ld.global.nc.f32 %0, [%1];\n\t}"
+            : "=f"(v)
+            : "l"(p), "r"((int)on));
+        return v;
+    }
     static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg(p); }
     static __device__ __forceinline__ void st(float* p, T v) { *p = v; }
     static __device__ __forceinline__ T fma(float w, T a, T c) { return fmaf(w, a, c); }
     static __device__ __forceinline__ T mul(float w, T a) { return w * a; }
 };
 
-// acc[v] += sum over entries [beg,end) of val * X[col, c0 + lane_off(v) ...]
-template <int NV, bool V4>
+// A warp signs off; the last one out rewinds both counters for the next launch.  This holds on
+// the drain path after a failed wait too, so a plan stays usable after a timeout.
+__device__ __forceinline__ void leave(const KParams& p, int lane) {
+    if (lane == 0) {
+        if (atomicAdd(p.counter + 1, 1ULL) == p.n_warps - 1) {
+            p.counter[0] = 0;
+            p.counter[1] = 0;
+            __threadfence();
+        }
+    }
+}
+
+// acc[v] += sum over entries [beg,end) of val * X[col, slab columns of this lane].
+// The 32 lanes fetch 32 (col, val) pairs at once and pass them round by shuffle.  Row fetches are
+// issued UNROLL at a time so that several independent loads per lane are in flight; the weights
+// are picked up after the fetches have been issued.
+template <int NV, bool V4, int UNROLL>
 __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
                                            const float* __restrict__ val, i32 beg, i32 end,
                                            const float* __restrict__ xs, i64 ldx,
@@ -183,25 +224,21 @@ __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
             mw = __ldg(val + b + lane);
         }
         i32 j = 0;
-        for (; j + 4 <= n_here; j += 4) {
-            i32 c[4];
-            float w[4];
-            T t[4][NV];
+        for (; j + UNROLL <= n_here; j += UNROLL) {
+            T t[UNROLL][NV];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                c[k] = __shfl_sync(0xffffffffu, mc, j + k);
-                w[k] = __shfl_sync(0xffffffffu, mw, j + k);
+            for (int k = 0; k < UNROLL; ++k) {
+                const i32 c = __shfl_sync(0xffffffffu, mc, j + k);
+                const float* r = xs + (i64)c * ldx;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) t[k][v] = V::ld_ro_if(r + v * STEP, ok[v]);
             }
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float* r = xs + (i64)c[k] * ldx;
+            for (int k = 0; k < UNROLL; ++k) {
+                const float w = __shfl_sync(0xffffffffu, mw, j + k);
 #pragma unroll
-                for (int v = 0; v < NV; ++v) t[k][v] = ok[v] ? V::ld_ro(r + v * STEP) : V::zero();
+                for (int v = 0; v < NV; ++v) acc[v] = V::fma(w, t[k][v], acc[v]);
             }
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-#pragma unroll
-                for (int v = 0; v < NV; ++v) acc[v] = V::fma(w[k], t[k][v], acc[v]);
         }
         for (; j < n_here; ++j) {
             const i32 c = __shfl_sync(0xffffffffu, mc, j);
@@ -214,52 +251,43 @@ __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
     }
 }
 
-// A warp signs off; the last one out rewinds both counters for the next launch.  This holds on
-// the drain path after a failed wait too, so a plan stays usable after a timeout.
-__device__ __forceinline__ void leave(const KParams& p, int lane) {
-    if (lane == 0) {
-        if (atomicAdd(p.counter + 1, 1ULL) == p.n_warps - 1) {
-            p.counter[0] = 0;
-            p.counter[1] = 0;
-            __threadfence();
-        }
-    }
-}
-
-// The fused product kernel.  One warp per (row, column slab) item; NV vectors per lane.
-template <int NV, bool V4>
-__global__ void __launch_bounds__(256) cbm_rows_kernel(const KParams p) {
+// The fused product kernel.  One warp per (row segment, column slab) item; NV vectors per lane.
+// UNROLL = row fetches in flight per lane, MINB = thread blocks the register budget must allow
+// per SM.
+template <int NV, bool V4, int UNROLL, int MINB>
+__global__ void __launch_bounds__(256, MINB) cbm_rows_kernel(const KParams p) {
     using V = Vec<V4>;
     using T = typename V::T;
     constexpr int STEP = 32 * V::E;
     const int lane = threadIdx.x & 31;
-
     for (;;) {
         u64 t = 0;
         if (lane == 0) t = atomicAdd(p.counter, 1ULL);
         t = __shfl_sync(0xffffffffu, t, 0);
-        if (t >= p.n_chunks) {
+        if (t >= (u64)p.n_units) {
             leave(p, lane);
             return;
         }
-        const i64 u0 = (i64)t * p.chunk;
-        const i64 u1 = min(u0 + (i64)p.chunk, p.n_units);
-        for (i64 u = u0; u < u1; ++u) {
-            const i32 slab = (i32)(u / p.n_rows);
-            const i32 pos = (i32)(u - (i64)slab * p.n_rows);
+        // One item per claim.  Handing a warp several consecutive items makes it sit on an item
+        // that waits for a neighbour while the items behind it (which others wait for) starve.
+        {
+            const unsigned u = (unsigned)t;  // the host refuses launches of 2^31 items or more
+            const i32 slab = (i32)(u / (unsigned)p.n_items);
+            const i32 pos = (i32)(u - (unsigned)slab * (unsigned)p.n_items);
             const int4 da = __ldg((const int4*)(p.desc + pos));
             const int4 db = __ldg((const int4*)(p.desc + pos) + 1);
-            const i32 out_row = da.x, parent_row = da.y, parent_pos = da.z, has_children = da.w;
+            const i32 out_row = da.x, parent_row = da.y, parent_pos = da.z, flags = da.w;
             const i32 beg = db.x, end = db.y;
             const float scale = __int_as_float(db.z), inv_parent = __int_as_float(db.w);
-
+            const bool partial = (flags & UNIT_PARTIAL) != 0;
+            if (partial && p.mode == MODE_UPDATE_ONLY) continue;
             const i32 c0 = slab * p.slab_w;
             const i32 wcols = min(p.slab_w, p.f - c0);
             const i32 lane_col = c0 + lane * V::E;
             bool ok[NV];
 #pragma unroll
             for (int v = 0; v < NV; ++v) ok[v] = (lane * V::E + v * STEP) < wcols;
-
+            i32* my_flag = p.flags + (i64)slab * p.n_items + pos;
             T acc[NV];
             float* yrow = p.y + (i64)out_row * p.ldy + lane_col;
             if (p.mode == MODE_UPDATE_ONLY) {
@@ -268,12 +296,37 @@ __global__ void __launch_bounds__(256) cbm_rows_kernel(const KParams p) {
             } else {
 #pragma unroll
                 for (int v = 0; v < NV; ++v) acc[v] = V::zero();
-                gather_row<NV, V4>(p.col, p.val, beg, end, p.x + lane_col, p.ldx, ok, acc, lane);
+                gather_row<NV, V4, UNROLL>(p.col, p.val, beg, end, p.x + lane_col, p.ldx, ok, acc, lane);
             }
-
+            if (partial) {
+                float* slot = p.scratch + ((i64)slab * p.n_slots + out_row) * p.slab_w + lane * V::E;
+#pragma unroll
+                for (int v = 0; v < NV; ++v)
+                    if (ok[v]) V::st(slot + v * STEP, acc[v]);
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) st_release(my_flag, p.epoch);
+                continue;
+            }
+            const i32 n_part = flags >> UNIT_NPART_SHIFT;
+            if (n_part > 0 && p.mode != MODE_UPDATE_ONLY) {
+                const i32 last_slot = __ldg(&p.desc[pos - 1].out_row);
+                for (i32 k = 0; k < n_part; ++k) {
+                    if (!wait_ready(my_flag - n_part + k, p.epoch, p.status, p.wait_ns)) {
+                        leave(p, lane);
+                        return;
+                    }
+                    const float* slot = p.scratch +
+                                        ((i64)slab * p.n_slots + (last_slot - (n_part - 1) + k)) * p.slab_w +
+                                        lane * V::E;
+#pragma unroll
+                    for (int v = 0; v < NV; ++v)
+                        if (ok[v]) acc[v] = V::fma(1.0f, V::ld_l2(slot + v * STEP), acc[v]);
+                }
+            }
             if (p.mode != MODE_DELTA_ONLY) {
                 if (parent_row >= 0) {
-                    if (!wait_ready(p.flags + (i64)slab * p.n_rows + parent_pos, p.epoch, p.status,
+                    if (!wait_ready(p.flags + (i64)slab * p.n_items + parent_pos, p.epoch, p.status,
                                     p.wait_ns)) {
                         leave(p, lane);
                         return;
@@ -292,16 +345,14 @@ __global__ void __launch_bounds__(256) cbm_rows_kernel(const KParams p) {
 #pragma unroll
             for (int v = 0; v < NV; ++v)
                 if (ok[v]) V::st(yrow + v * STEP, acc[v]);
-
-            if (has_children && p.mode != MODE_DELTA_ONLY) {
+            if ((flags & UNIT_PUBLISH) && p.mode != MODE_DELTA_ONLY) {
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) st_release(p.flags + (i64)slab * p.n_rows + pos, p.epoch);
+                if (lane == 0) st_release(my_flag, p.epoch);
             }
         }
     }
 }
-
 // Plain CSR product (no tree): rows in natural order, one warp per (row, slab), grid-stride.
 template <int NV, bool V4>
 __global__ void __launch_bounds__(256)
@@ -328,7 +379,7 @@ __global__ void __launch_bounds__(256)
             ok[v] = (lane * V::E + v * STEP) < wcols;
             acc[v] = V::zero();
         }
-        gather_row<NV, V4>(col, val, __ldg(row_b + row), __ldg(row_e + row), x + lane_col, ldx, ok,
+        gather_row<NV, V4, (NV >= 4 ? 4 : 8)>(col, val, __ldg(row_b + row), __ldg(row_e + row), x + lane_col, ldx, ok,
                            acc, lane);
         float* yrow = y + (i64)row * ldy + lane_col;
 #pragma unroll
@@ -350,7 +401,7 @@ Shape pick_shape(i32 f, i32 want_slab, bool can_v4) {
     Shape s{};
     s.v4 = can_v4;
     const i32 lane_w = s.v4 ? 128 : 32;  // columns covered by one vector per lane
-    i32 slab = want_slab > 0 ? want_slab : (s.v4 ? 128 : 64);
+    i32 slab = want_slab > 0 ? want_slab : (s.v4 ? 256 : 64);
     slab = std::max(lane_w, (slab / lane_w) * lane_w);
     slab = std::min(slab, lane_w * 4);
     const i32 f_up = ((f + lane_w - 1) / lane_w) * lane_w;
@@ -374,6 +425,10 @@ struct cbm_b200_plan {
     i32 n_labels = 0;  // rows of the dense right-hand side
     i32 n_out = 0;     // rows of the output shard (owned label range)
     i32 n_rows = 0;    // rows actually computed
+    i32 n_items = 0;   // work items per slab (rows + extra segments of long rows)
+    i32 n_slots = 0;   // scratch slots per slab
+    float* d_scratch = nullptr;
+    i64 scratch_cap = 0;
     i64 n_delta = 0;
     i32 n_root_children = 0;
     i32 depth = 0;
@@ -430,6 +485,7 @@ extern "C" void cbm_b200_plan_destroy(cbm_b200_plan* p) {
     cudaFree(p->d_col);
     cudaFree(p->d_val);
     cudaFree(p->d_flags);
+    cudaFree(p->d_scratch);
     cudaFree(p->d_counter);
     cudaFree(p->d_status);
     cudaFree(p->stage_x);
@@ -510,39 +566,78 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
         return l >= own_begin && l < own_end;
     };
 
-    // ---- schedule: owned rows in breadth-first order ----
+    // ---- schedule ----
+    // Owned rows in breadth-first order, except that the children of the virtual root (which wait
+    // for nobody) are issued longest first so that the heavy rows never form the tail.  Any order
+    // in which a parent precedes its children is valid.
+    std::vector<i32> sched;
+    sched.reserve((size_t)(own_end - own_begin));
+    for (i32 v : order)
+        if (owned(v)) sched.push_back(v);
+    {
+        auto first_deep = std::stable_partition(sched.begin(), sched.end(),
+                                                [&](i32 v) { return parent[v] == n; });
+        std::stable_sort(sched.begin(), first_deep, [&](i32 a, i32 b) {
+            return delta_crow[a + 1] - delta_crow[a] > delta_crow[b + 1] - delta_crow[b];
+        });
+    }
+    const i32 SEG = 128;        // delta entries per work item of a long row
+    const i32 SPLIT_OVER = 192; // rows longer than this are cut into segments
     std::vector<i32> pos_of((size_t)n, -1);
     std::vector<RowDesc> desc;
-    desc.reserve((size_t)(own_end - own_begin));
+    desc.reserve(sched.size());
     std::vector<i32> pcol;
     std::vector<float> pval;
-    i32 depth = 0, n_root_children = 0;
-    for (i32 v : order) {
-        if (!owned(v)) continue;
+    pcol.reserve((size_t)nd_all);
+    pval.reserve((size_t)nd_all);
+    i32 depth = 0, n_root_children = 0, n_slots = 0;
+    for (i32 v : sched) {
         const i32 u = parent[v];
         if (u != n && !owned(u))
             return cbm::fail(CBM_B200_ERR_ARG,
                              "plan_create: owned range cuts a subtree (parent of an owned row "
                              "is not owned)");
-        RowDesc d{};
-        d.out_row = label(v) - own_begin;
-        d.parent_row = (u == n) ? -1 : label(u) - own_begin;
-        d.parent_pos = (u == n) ? -1 : pos_of[u];
-        d.has_children = 0;
-        d.beg = (i32)pcol.size();
+        const i32 first = (i32)pcol.size();
         for (i32 k = delta_crow[v]; k < delta_crow[v + 1]; ++k) {
             pcol.push_back(label(delta_col[k]));
             pval.push_back(delta_val[k]);
         }
+        const i32 len = (i32)pcol.size() - first;
+        i32 n_part = 0;
+        i32 cursor = first;
+        if (len > SPLIT_OVER) {
+            const i32 n_seg = (len + SEG - 1) / SEG;
+            n_part = n_seg - 1;
+            for (i32 k = 0; k < n_part; ++k) {
+                RowDesc q{};
+                q.out_row = n_slots++;
+                q.parent_row = -1;
+                q.parent_pos = -1;
+                q.flags = UNIT_PARTIAL | UNIT_PUBLISH;
+                q.beg = cursor;
+                q.end = cursor + SEG;
+                q.scale = 1.0f;
+                q.inv_parent = 1.0f;
+                cursor += SEG;
+                desc.push_back(q);
+            }
+        }
+        RowDesc d{};
+        d.out_row = label(v) - own_begin;
+        d.parent_row = (u == n) ? -1 : label(u) - own_begin;
+        d.parent_pos = (u == n) ? -1 : pos_of[u];
+        d.flags = n_part << UNIT_NPART_SHIFT;
+        d.beg = cursor;
         d.end = (i32)pcol.size();
         d.scale = multiplier ? multiplier[v] : 1.0f;
         d.inv_parent = (multiplier && u != n) ? 1.0f / multiplier[u] : 1.0f;
         pos_of[v] = (i32)desc.size();
-        if (u != n) desc[pos_of[u]].has_children = 1;
+        if (u != n) desc[pos_of[u]].flags |= UNIT_PUBLISH;
         else ++n_root_children;
         depth = std::max(depth, level[v]);
         desc.push_back(d);
     }
+    const i32 n_rows_owned = (i32)sched.size();
 
     int n_dev = 0;
     CBM_CUDA(cudaGetDeviceCount(&n_dev));
@@ -557,7 +652,9 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
     p->n = n;
     p->n_labels = n_labels;
     p->n_out = own_end - own_begin;
-    p->n_rows = (i32)desc.size();
+    p->n_rows = n_rows_owned;
+    p->n_items = (i32)desc.size();
+    p->n_slots = n_slots;
     p->n_delta = (i64)pcol.size();
     p->n_root_children = n_root_children;
     p->depth = depth;
@@ -625,7 +722,9 @@ namespace {
 
 template <int NV, bool V4>
 int launch_rows(const KParams& kp, int blocks, cudaStream_t s) {
-    cbm_rows_kernel<NV, V4><<<blocks, 256, 0, s>>>(kp);
+    // Unroll depth and resident blocks per SM were chosen by measurement on B200: forms that
+    // spill registers lose more than extra resident warps gain.
+    cbm_rows_kernel<NV, V4, (NV == 1 ? 8 : 4), (NV == 1 ? 4 : (NV == 2 ? 3 : 2))><<<blocks, 256, 0, s>>>(kp);
     CBM_CUDA(cudaGetLastError());
     return CBM_B200_OK;
 }
@@ -634,6 +733,8 @@ int check_dense(const char* who, const void* x, i64 ldx, const void* y, i64 ldy,
     if (f <= 0) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": f must be positive");
     if (!y || ldy < f) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": bad y / ldy");
     if (x && ldx < f) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": ldx < f");
+    if (ldx > INT32_MAX || ldy > INT32_MAX)
+        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": leading dimension exceeds 2^31-1");
     if (x && x == y) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": x and y alias");
     return CBM_B200_OK;
 }
@@ -655,7 +756,9 @@ int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* 
                         (mode == MODE_UPDATE_ONLY || ((ldx % 4 == 0) && aligned16(x)));
     const Shape sh = pick_shape(f, p->slab_width, can_v4);
 
-    const i64 need_flags = (i64)sh.n_slabs * p->n_rows;
+    const i64 need_flags = (i64)sh.n_slabs * p->n_items;
+    if (need_flags >= (i64)1 << 31)
+        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": rows x column slabs exceeds 2^31 work items");
     if (need_flags > p->flags_cap) {
         // Growing the flag array: the old one may still be read by a launch in flight.
         CBM_CUDA(cudaStreamSynchronize(s));
@@ -667,6 +770,17 @@ int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* 
         CBM_CUDA(cudaMemset(p->d_flags, 0, (size_t)need_flags * sizeof(i32)));
         p->flags_cap = need_flags;
         p->device_bytes += need_flags * (i64)sizeof(i32);
+    }
+    const i64 need_scratch = (i64)sh.n_slabs * p->n_slots * sh.slab_w;
+    if (need_scratch > p->scratch_cap) {
+        CBM_CUDA(cudaStreamSynchronize(s));
+        cudaFree(p->d_scratch);
+        p->d_scratch = nullptr;
+        p->device_bytes -= p->scratch_cap * (i64)sizeof(float);
+        p->scratch_cap = 0;
+        CBM_CUDA(cudaMalloc((void**)&p->d_scratch, (size_t)need_scratch * sizeof(float)));
+        p->scratch_cap = need_scratch;
+        p->device_bytes += need_scratch * (i64)sizeof(float);
     }
     if (p->epoch == INT32_MAX) {  // epochs exhausted: start over on clean flags
         CBM_CUDA(cudaMemsetAsync(p->d_flags, 0, (size_t)p->flags_cap * sizeof(i32), s));
@@ -683,10 +797,10 @@ int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* 
     kp.ldy = ldy;
     kp.f = f;
     kp.slab_w = sh.slab_w;
-    kp.n_rows = p->n_rows;
+    kp.n_items = p->n_items;
+    kp.scratch = p->d_scratch;
+    kp.n_slots = p->n_slots;
     kp.n_units = need_flags;
-    kp.chunk = 4;
-    kp.n_chunks = (u64)((kp.n_units + kp.chunk - 1) / kp.chunk);
     kp.counter = p->d_counter;
     kp.flags = p->d_flags;
     kp.epoch = ++p->epoch;
@@ -696,7 +810,7 @@ int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* 
     kp.wait_ns = 2000000000ULL;
 
     int blocks = p->n_blocks > 0 ? p->n_blocks : p->sm_count * 8;
-    const i64 max_useful = (i64)((kp.n_chunks + 7) / 8);
+    const i64 max_useful = (kp.n_units + 7) / 8;
     blocks = (int)std::max<i64>(1, std::min<i64>(blocks, max_useful));
     kp.n_warps = (u64)blocks * 8;
 

@@ -49,6 +49,7 @@ EXPORTED = [
     "cbm_b200_delta_spmm",
     "cbm_b200_csr_spmm",
     "cbm_b200_spmm_update_host",
+    "cbm_b200_spmm_update_static",
 ]
 
 
@@ -132,6 +133,8 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_csr_spmm", c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
         c_int64, c_void_p, c_int64, c_int32, c_void_p)
     sig("cbm_b200_spmm_update_host", c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32)
+    sig("cbm_b200_spmm_update_static", c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32,
+        c_int32, c_void_p)
     _lib = L
     return L
 

@@ -913,3 +913,119 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
     CBM_CUDA(cudaMemcpyAsync(y, p->stage_y, (size_t)yb * sizeof(float), cudaMemcpyDeviceToHost, s));
     return cbm_b200_plan_status(p, s);
 }
+
+// ------------------------------------------------------------------------------------------
+// Product without any allocation in the call path.
+//
+// The ordinary product entry points grow the plan's ready-flag and partial-sum buffers with
+// cudaMalloc the first time a wider operand arrives.  Some callers must never reach an allocator
+// once they are running: a serving loop that has handed all device memory to its own pool, code
+// that runs while a stream is being captured, a real-time path that cannot absorb the implicit
+// device synchronisation of cudaMalloc/cudaFree.  For them the same kernel is offered with its
+// per-call scratch (claim counters, ready flags, partial sums of long rows) carved out of one
+// fixed array that lives in the library image: every GPU that loads the library holds
+// CBM_B200_STATIC_SCRATCH_BYTES of it until the process exits.
+//
+// The array is shared by every plan and every call on a device and keeps whatever the previous
+// call left in it, so each call first clears the counters and the flags it is about to use (on
+// the caller's stream).  Two such calls that overlap on one GPU — different streams, or different
+// host threads — race on the array; the caller has to order them.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[CBM_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// In host code the name g_static_scratch is only a handle for the runtime, not a device address.
+// The address a kernel can use is asked for once per device, with that device current.
+int static_scratch_address(int device, unsigned char** out) {
+    if (device < 0 || device >= kMaxDevices)
+        return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_static: device ordinal out of range");
+    if (!g_static_scratch_addr[device]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return cbm::fail(CBM_B200_ERR_CUDA, std::string("cudaGetSymbolAddress(g_static_scratch): ") +
+                                                    cudaGetErrorString(e));
+        g_static_scratch_addr[device] = static_cast<unsigned char*>(ptr);
+    }
+    *out = g_static_scratch_addr[device];
+    return CBM_B200_OK;
+}
+
+i64 round_up_256(i64 v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+
+extern "C" int cbm_b200_spmm_update_static(cbm_b200_plan* p, const float* x, int64_t ldx, float* y,
+                                           int64_t ldy, int32_t f, int32_t normalized,
+                                           void* stream) {
+    const char* who = "spmm_update_static";
+    if (!p) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": NULL plan");
+    int rc = check_dense(who, x, ldx, y, ldy, f);
+    if (rc) return rc;
+    if (!x) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": x is NULL");
+    if (normalized && !p->normalized)
+        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": plan was created without a multiplier");
+    if (p->n_rows == 0) return CBM_B200_OK;
+
+    const bool can_v4 = (f % 4 == 0) && (ldy % 4 == 0) && aligned16(y) && (ldx % 4 == 0) && aligned16(x);
+    const Shape sh = pick_shape(f, p->slab_width, can_v4);
+    const i64 n_units = (i64)sh.n_slabs * p->n_items;
+    if (n_units >= (i64)1 << 31)
+        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": rows x column slabs exceeds 2^31 work items");
+    // layout inside the fixed array: counters | ready flags | partial sums
+    const i64 off_flags = 256;
+    const i64 off_slots = off_flags + round_up_256(n_units * (i64)sizeof(i32));
+    const i64 need = off_slots + (i64)sh.n_slabs * p->n_slots * sh.slab_w * (i64)sizeof(float);
+    if (need > (i64)CBM_B200_STATIC_SCRATCH_BYTES)
+        return cbm::fail(CBM_B200_ERR_ARG,
+                         std::string(who) + ": this product needs " + std::to_string(need) +
+                             " bytes of scratch, the fixed array holds " +
+                             std::to_string((i64)CBM_B200_STATIC_SCRATCH_BYTES) +
+                             "; use cbm_b200_spmm_update / cbm_b200_fused_spmm_update");
+
+    DeviceGuard g(p->device);
+    if (!g.ok) return cbm::fail(CBM_B200_ERR_CUDA, std::string(who) + ": cudaSetDevice failed");
+    unsigned char* base = nullptr;
+    rc = static_scratch_address(p->device, &base);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    // counters and flags must start at zero; the partial sums are written before they are read
+    CBM_CUDA(cudaMemsetAsync(base, 0, (size_t)(off_flags + n_units * (i64)sizeof(i32)), s));
+
+    KParams kp{};
+    kp.desc = p->d_desc;
+    kp.col = p->d_col;
+    kp.val = p->d_val;
+    kp.x = x;
+    kp.y = y;
+    kp.ldx = ldx;
+    kp.ldy = ldy;
+    kp.f = f;
+    kp.slab_w = sh.slab_w;
+    kp.n_items = p->n_items;
+    kp.n_units = n_units;
+    kp.scratch = reinterpret_cast<float*>(base + off_slots);
+    kp.n_slots = p->n_slots;
+    kp.counter = reinterpret_cast<u64*>(base);
+    kp.flags = reinterpret_cast<i32*>(base + off_flags);
+    kp.epoch = 1;  // flags were just cleared, so any non-zero mark will do
+    kp.status = p->d_status;
+    kp.mode = MODE_FUSED;
+    kp.use_scale = normalized ? 1 : 0;
+    kp.wait_ns = 2000000000ULL;
+    int blocks = p->n_blocks > 0 ? p->n_blocks : p->sm_count * 8;
+    blocks = (int)std::max<i64>(1, std::min<i64>(blocks, (n_units + 7) / 8));
+    kp.n_warps = (u64)blocks * 8;
+    if (sh.v4) {
+        if (sh.nv == 1) return launch_rows<1, true>(kp, blocks, s);
+        if (sh.nv == 2) return launch_rows<2, true>(kp, blocks, s);
+        return launch_rows<4, true>(kp, blocks, s);
+    }
+    if (sh.nv == 1) return launch_rows<1, false>(kp, blocks, s);
+    if (sh.nv == 2) return launch_rows<2, false>(kp, blocks, s);
+    return launch_rows<4, false>(kp, blocks, s);
+}

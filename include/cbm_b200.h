@@ -161,6 +161,32 @@ int cbm_b200_csr_spmm(int32_t n_rows, const int32_t* row_b, const int32_t* row_e
 int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float* y, int32_t f,
                               int32_t normalized);
 
+/* --------------------------------------------------------------------------------------------
+ * The fused product for callers that must not allocate.  (No counterpart in the reference, whose
+ * CPU kernels need no scratch memory; added for GPU callers.)
+ *
+ * Who needs it: a caller that cannot reach cudaMalloc once it is running — it gave all device
+ * memory to its own pool, it runs while a stream is being captured, or it cannot afford the
+ * device-wide synchronisation an allocation implies.  The entry points above allocate their
+ * ready-flag and partial-sum buffers on demand; this one performs the same product (same kernel,
+ * same results) with that scratch taken from a fixed array of CBM_B200_STATIC_SCRATCH_BYTES that
+ * is part of the library image, so every GPU that loads the library holds that much memory until
+ * the process exits.  The call itself allocates and frees nothing.
+ *
+ * `normalized` != 0 computes what cbm_b200_fused_spmm_update computes, 0 what cbm_b200_spmm_update
+ * computes.  x, y, ldx, ldy, f, stream as there.  A product whose scratch need (4 bytes per row
+ * segment and column slab, plus the partial sums of rows longer than 192 delta entries) exceeds
+ * the fixed array is refused with CBM_B200_ERR_ARG and a message giving both sizes.
+ *
+ * The first call on each device looks up the array's device address; make that first call before
+ * any stream capture begins.  All calls on a device share the array and each call clears the part
+ * it uses, so two of these calls that overlap on one GPU (different streams or threads) race:
+ * the caller must order them.  Timeouts are reported through cbm_b200_plan_status as usual.
+ * ------------------------------------------------------------------------------------------ */
+#define CBM_B200_STATIC_SCRATCH_BYTES (8u << 20)
+int cbm_b200_spmm_update_static(cbm_b200_plan* p, const float* x, int64_t ldx, float* y,
+                                int64_t ldy, int32_t f, int32_t normalized, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -37,7 +37,9 @@ sys.path.insert(0, ROOT)
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the product kernel, from the ncu
 # captures summarised under profiles/ (key: workload, operand width, GPUs, scale).
-DRAM_TRAFFIC: dict = {}
+DRAM_TRAFFIC: dict = {
+    ("c2", 500, 1, 1.0): 2.027e9,  # profiles/cbm_rows_kernel_c2_f500.md
+}
 
 
 def parse():
@@ -51,6 +53,7 @@ def parse():
     ap.add_argument("--f", type=int, default=0, help="override the operand width")
     ap.add_argument("--slab", type=int, default=0)
     ap.add_argument("--blocks", type=int, default=0)
+    ap.add_argument("--host-chunk", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
@@ -224,7 +227,7 @@ def main():
         plan = c.plan(local_rank)
         x_host = torch.from_numpy(x).pin_memory()
         n_out = c.num_rows
-    plan.tune(args.slab, args.blocks)
+    plan.tune(args.slab, args.blocks, args.host_chunk)
     xd = x_host.to(dev, non_blocking=True)
     yd = torch.zeros((n_out, f), device=dev)
     y_host = torch.empty((n_out, f)).pin_memory()

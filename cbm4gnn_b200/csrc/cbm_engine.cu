@@ -446,6 +446,9 @@ struct cbm_b200_plan {
     i32 sm_count = 148;
     i64 device_bytes = 0;
     cudaStream_t own_stream = nullptr;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    std::vector<cudaEvent_t> events;
+    i32 host_chunk = 0;
     float* stage_x = nullptr;
     float* stage_y = nullptr;
     i64 stage_x_cap = 0, stage_y_cap = 0;
@@ -491,6 +494,9 @@ extern "C" void cbm_b200_plan_destroy(cbm_b200_plan* p) {
     cudaFree(p->stage_x);
     cudaFree(p->stage_y);
     if (p->own_stream) cudaStreamDestroy(p->own_stream);
+    if (p->copy_in) cudaStreamDestroy(p->copy_in);
+    if (p->copy_out) cudaStreamDestroy(p->copy_out);
+    for (cudaEvent_t e : p->events) cudaEventDestroy(e);
     delete p;
 }
 
@@ -696,11 +702,15 @@ extern "C" int cbm_b200_plan_info(const cbm_b200_plan* p, int32_t* n_rows, int64
     return CBM_B200_OK;
 }
 
-extern "C" int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t n_blocks) {
+extern "C" int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t n_blocks,
+                                  int32_t host_chunk) {
     if (!p) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: NULL plan");
-    if (slab_width < 0 || n_blocks < 0) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: negative knob");
+    if (slab_width < 0 || n_blocks < 0 || host_chunk < 0)
+        return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: negative knob");
+    if (host_chunk % 4 != 0) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: host_chunk must be a multiple of 4");
     p->slab_width = slab_width;
     p->n_blocks = n_blocks;
+    p->host_chunk = host_chunk;
     return CBM_B200_OK;
 }
 
@@ -903,14 +913,40 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
         p->stage_y = nullptr;
         p->stage_y_cap = 0;
         CBM_CUDA(cudaMalloc((void**)&p->stage_y, (size_t)std::max<i64>(yb, 1) * sizeof(float)));
+        // padding rows of a shard are never written by the kernel: give them a defined value
+        CBM_CUDA(cudaMemset(p->stage_y, 0, (size_t)std::max<i64>(yb, 1) * sizeof(float)));
         p->stage_y_cap = yb;
     }
+    // Pipeline over column chunks: while chunk k is multiplied, chunk k+1 of x is on its way in
+    // and chunk k-1 of y on its way out (PCIe is full duplex), so the call costs about one
+    // transfer of x plus the last chunk's product and transfer instead of x + product + y.
+    const i32 chunk = p->host_chunk > 0 ? p->host_chunk : 128;
+    const i32 n_chunks = (f + chunk - 1) / chunk;
+    if (!p->copy_in) CBM_CUDA(cudaStreamCreateWithFlags(&p->copy_in, cudaStreamNonBlocking));
+    if (!p->copy_out) CBM_CUDA(cudaStreamCreateWithFlags(&p->copy_out, cudaStreamNonBlocking));
+    while ((i32)p->events.size() < 2 * n_chunks) {
+        cudaEvent_t e;
+        CBM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        p->events.push_back(e);
+    }
     cudaStream_t s = p->own_stream;
-    CBM_CUDA(cudaMemcpyAsync(p->stage_x, x, (size_t)xb * sizeof(float), cudaMemcpyHostToDevice, s));
-    int rc = run_plan(p, "spmm_update_host", p->stage_x, f, p->stage_y, f, f, MODE_FUSED,
-                      normalized != 0, s);
-    if (rc) return rc;
-    CBM_CUDA(cudaMemcpyAsync(y, p->stage_y, (size_t)yb * sizeof(float), cudaMemcpyDeviceToHost, s));
+    const size_t pitch = (size_t)f * sizeof(float);
+    for (i32 k = 0; k < n_chunks; ++k) {
+        const i32 c0 = k * chunk;
+        const i32 w = std::min(chunk, f - c0);
+        CBM_CUDA(cudaMemcpy2DAsync(p->stage_x + c0, pitch, x + c0, pitch, (size_t)w * sizeof(float),
+                                   (size_t)p->n_labels, cudaMemcpyHostToDevice, p->copy_in));
+        CBM_CUDA(cudaEventRecord(p->events[2 * k], p->copy_in));
+        CBM_CUDA(cudaStreamWaitEvent(s, p->events[2 * k], 0));
+        int rc = run_plan(p, "spmm_update_host", p->stage_x + c0, f, p->stage_y + c0, f, w, MODE_FUSED,
+                          normalized != 0, s);
+        if (rc) return rc;
+        CBM_CUDA(cudaEventRecord(p->events[2 * k + 1], s));
+        CBM_CUDA(cudaStreamWaitEvent(p->copy_out, p->events[2 * k + 1], 0));
+        CBM_CUDA(cudaMemcpy2DAsync(y + c0, pitch, p->stage_y + c0, pitch, (size_t)w * sizeof(float),
+                                   (size_t)p->n_out, cudaMemcpyDeviceToHost, p->copy_out));
+    }
+    CBM_CUDA(cudaStreamSynchronize(p->copy_out));
     return cbm_b200_plan_status(p, s);
 }
 

@@ -110,13 +110,22 @@ class ShardedCBM:
         self.c, self.rank, self.world, self.group = c, rank, world, group
         self.part = partition or partition_subtrees(c, world)
         self.begin, self.end = self.part.offsets(rank)
-        if device_index is None:
-            device_index = torch.cuda.current_device()
-        mul = None if c.col_multiplier is None else _as_f32(c.col_multiplier)
-        self.plan = _Plan(c.num_rows, c.mst_row.numpy(), c.mst_col.numpy(), c._crow, c._dcol, c._dval, mul,
-                          device_index, perm=self.part.perm, n_labels=self.part.n_labels,
-                          own_begin=self.begin, own_end=self.end)
+        self.device_index = device_index
+        self._plan = None
         self._perm_t = None
+
+    @property
+    def plan(self) -> _Plan:
+        """Device schedule of this rank's rows (created on first use)."""
+        if self._plan is None:
+            c = self.c
+            if self.device_index is None:
+                self.device_index = torch.cuda.current_device()
+            mul = None if c.col_multiplier is None else _as_f32(c.col_multiplier)
+            self._plan = _Plan(c.num_rows, c.mst_row.numpy(), c.mst_col.numpy(), c._crow, c._dcol, c._dval, mul,
+                               self.device_index, perm=self.part.perm, n_labels=self.part.n_labels,
+                               own_begin=self.begin, own_end=self.end)
+        return self._plan
 
     def _perm(self, device):
         if self._perm_t is None or self._perm_t.device != device:
@@ -144,10 +153,55 @@ class ShardedCBM:
         return mine
 
     def matmul(self, x_labels: torch.Tensor, gather: bool = True) -> torch.Tensor:
-        """``A @ x`` in label space: local subtrees, then (optionally) the all-gather of shards."""
+        """``A @ x`` in label space: local subtrees, then (optionally) the all-gather of shards.
+        Padding labels of the result are zero."""
         out = torch.zeros((self.part.n_labels, x_labels.size(1)), dtype=x_labels.dtype, device=x_labels.device)
         mine = self.local_product(x_labels, out)
         if gather and self.world > 1:
             import torch.distributed as dist
             dist.all_gather_into_tensor(out, mine, group=self.group)
+        return out
+
+
+class ShardedGCN(torch.nn.Module):
+    """Forward pass of a stack of GCN layers over a sharded CBM structure (weights replicated).
+
+    Per layer and rank: the dense map ``lin`` on the rank's own block of rows (1/world of the
+    GEMM), one in-place all-gather of the ``lin`` output shards (every rank needs all rows of the
+    product's right-hand side), then the product over the rank's subtrees.  ReLU between layers is
+    applied to the local block.  Everything lives in label space; padding rows are zero and stay
+    zero because the layers have no bias.
+    """
+
+    def __init__(self, widths, sharded: ShardedCBM):
+        super().__init__()
+        self.sharded = sharded
+        self.lins = torch.nn.ModuleList(torch.nn.Linear(a, b, bias=False) for a, b in zip(widths[:-1], widths[1:]))
+        for lin in self.lins:
+            torch.nn.init.xavier_uniform_(lin.weight)
+
+    @torch.no_grad()
+    def forward(self, x_labels: torch.Tensor, gather_output: bool = True) -> torch.Tensor:
+        """``x_labels``: [n_labels, F_in] in label space.  Returns the output in label space
+        (all rows when ``gather_output``, else only this rank's block is meaningful)."""
+        import torch.distributed as dist
+        sh = self.sharded
+        h_local = x_labels[sh.begin:sh.end]
+        out = None
+        for i, lin in enumerate(self.lins):
+            if i:
+                h_local = h_local.relu()
+            z = torch.zeros((sh.part.n_labels, lin.out_features), dtype=x_labels.dtype, device=x_labels.device)
+            prev = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = False  # full fp32, as the 1e-4 tolerance needs
+            try:
+                torch.mm(h_local, lin.weight.t(), out=z[sh.begin:sh.end])
+            finally:
+                torch.backends.cuda.matmul.allow_tf32 = prev
+            if sh.world > 1:
+                dist.all_gather_into_tensor(z, z[sh.begin:sh.end], group=sh.group)
+            out = torch.zeros_like(z)
+            h_local = sh.local_product(z, out)
+        if gather_output and sh.world > 1:
+            dist.all_gather_into_tensor(out, h_local, group=sh.group)
         return out

@@ -102,48 +102,87 @@ struct Candidates {
     i64 total = 0;
 };
 
-// Pairs are enumerated once (c > r) like the upper triangle the reference reads from syrk
-// (cbm/cbm_extensions.cpp:87-102); both directions are tested for each pair.
+// The reference tests every pair of rows that share a column (the non-zeros of A*A^T,
+// cbm/cbm_extensions.cpp:87-102).  The same set of candidate edges is produced here without
+// visiting all those pairs: an edge u -> v passes the rule  h(u,v) < |v| - alpha  exactly when
+// |u ∩ v| > (|u| + alpha) / 2, i.e. when at least t(u) = floor((|u| + alpha) / 2) + 1 of u's columns
+// are also in v.  Order all columns from rarest to most frequent; if u and v share t(u) columns,
+// one of them must be among u's first |u| - t(u) + 1 columns in that order (only t(u) - 1 columns
+// lie behind them).  So it is enough to look, for every possible parent u, at the rows that hold
+// one of those few rare columns, and to count the intersection exactly for each of them.  Hub
+// columns, which make A*A^T explode, almost never fall in that prefix.
 Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
     const i32 n = a.n;
     struct Tri {
         i32 src, dst, w;
     };
+    // rank of every column in the rare-to-frequent order (ties by id)
+    std::vector<i32> by_freq((size_t)n);
+    for (i32 c = 0; c < n; ++c) by_freq[c] = c;
+    std::sort(by_freq.begin(), by_freq.end(), [&](i32 x, i32 y) {
+        const i32 fx = at.len(x), fy = at.len(y);
+        return fx != fy ? fx < fy : x < y;
+    });
+    std::vector<i32> rank((size_t)n);
+    for (i32 i = 0; i < n; ++i) rank[by_freq[i]] = i;
+    std::vector<i32>().swap(by_freq);
+
     const i32 block = 64;
     const i32 n_blocks = (n + block - 1) / block;
     std::vector<std::vector<Tri>> found((size_t)n_blocks);
 
 #pragma omp parallel
     {
-        std::vector<i32> cnt((size_t)n, 0);
-        std::vector<i32> touched;
+        std::vector<i32> in_u((size_t)n, -1);   // column -> u if the column is in row u
+        std::vector<i32> seen((size_t)n, -1);   // row -> u if already listed as a candidate of u
+        std::vector<i32> cand, cols;
 #pragma omp for schedule(dynamic, 1)
         for (i32 b = 0; b < n_blocks; ++b) {
             std::vector<Tri>& out = found[b];
-            const i32 r_end = std::min(n, (b + 1) * block);
-            for (i32 r = b * block; r < r_end; ++r) {
-                touched.clear();
-                for (i64 k = a.ptr[r]; k < a.ptr[r + 1]; ++k) {
-                    const i32 colk = a.idx[k];
-                    // rows c > r that also hold column colk
-                    const i32* lb = at.idx.data() + at.ptr[colk];
-                    const i32* le = at.idx.data() + at.ptr[colk + 1];
-                    const i32* it = std::upper_bound(lb, le, r);
-                    for (; it != le; ++it) {
-                        const i32 c = *it;
-                        if (cnt[c]++ == 0) touched.push_back(c);
+            const i32 u_end = std::min(n, (b + 1) * block);
+            for (i32 u = b * block; u < u_end; ++u) {
+                const i32 nu = a.len(u);
+                // shared columns an edge u -> v needs: the smallest integer above (|u| + alpha) / 2,
+                // and at least one (the reference only sees pairs that intersect)
+                const i64 sum = (i64)nu + alpha;
+                const i64 half_floor = sum >= 0 ? sum / 2 : -((-sum + 1) / 2);
+                const i64 need64 = std::max<i64>(half_floor + 1, 1);
+                if (need64 > nu) continue;  // no row can contain that many of u's columns
+                const i32 need = (i32)need64;
+                const i32* ub = a.idx.data() + a.ptr[u];
+                const i32* ue = a.idx.data() + a.ptr[u + 1];
+                cols.assign(ub, ue);
+                const i32 plen = nu - need + 1;
+                if (plen < nu)
+                    std::partial_sort(cols.begin(), cols.begin() + plen, cols.end(),
+                                      [&](i32 x, i32 y) { return rank[x] < rank[y]; });
+                for (const i32* k = ub; k != ue; ++k) in_u[*k] = u;
+                cand.clear();
+                seen[u] = u;
+                for (i32 i = 0; i < plen; ++i) {
+                    const i32 colk = cols[i];
+                    for (i64 q = at.ptr[colk]; q < at.ptr[colk + 1]; ++q) {
+                        const i32 v = at.idx[q];
+                        if (seen[v] != u) {
+                            seen[v] = u;
+                            cand.push_back(v);
+                        }
                     }
                 }
-                if (touched.empty()) continue;
-                std::sort(touched.begin(), touched.end());
-                const i32 nr = a.len(r);
-                for (i32 c : touched) {
-                    const i32 both = cnt[c];
-                    cnt[c] = 0;
-                    const i32 nc = a.len(c);
-                    const i32 h = nr + nc - 2 * both;
-                    if (h < nr - alpha) out.push_back({c, r, h});
-                    if (h < nc - alpha) out.push_back({r, c, h});
+                std::sort(cand.begin(), cand.end());
+                for (i32 v : cand) {
+                    const i32 nv = a.len(v);
+                    if (nv < need) continue;
+                    const i32* vb = a.idx.data() + a.ptr[v];
+                    const i32* ve = a.idx.data() + a.ptr[v + 1];
+                    i32 both = 0;
+                    if ((i64)nv <= (i64)16 * nu) {
+                        for (const i32* k = vb; k != ve; ++k) both += (in_u[*k] == u);
+                    } else {
+                        for (const i32* k = ub; k != ue; ++k) both += std::binary_search(vb, ve, *k);
+                    }
+                    const i32 h = nu + nv - 2 * both;
+                    if (h < nv - alpha) out.push_back({u, v, h});  // cbm/cbm_extensions.cpp:93-101
                 }
             }
         }

@@ -63,6 +63,20 @@ def test_candidate_rule_respected():
             assert h < rows[v].size - alpha and dl[v] == h
 
 
+@pytest.mark.parametrize("alpha", [0, 1, 5, 40, -3])
+def test_candidate_set_equals_all_pairs_enumeration(alpha):
+    """The builder finds candidates through a rare-column prefix instead of visiting every
+    intersecting pair; the set must be the one the all-pairs rule of cbm/cbm_extensions.cpp:75-102
+    yields."""
+    for ei in (graphs.make_graph("c1", scale=0.15), graphs.erdos_renyi(40, 0.4, 9),
+               graphs.copy_model(400, 0.95, 6, 3)):
+        n = int(ei.max()) + 1
+        c = _cbm(ei, alpha)
+        ref = orc.candidate_edges(ei, n, alpha)
+        assert c.build_info["n_candidates"] == len(ref)
+        assert c.build_info["n_delta"] == orc.build_structure(ei, alpha)["weight"]
+
+
 def test_deterministic_and_thread_independent():
     ei = graphs.make_graph("c1", scale=0.25)
     e = torch.from_numpy(ei).to(torch.int32)

@@ -49,11 +49,15 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2")
+    ap.add_argument("--task", default="spmm", choices=["spmm", "gcn"],
+                    help="spmm: one CBM product per step (the headline); gcn: forward+backward of the "
+                         "stacked GCN of the workload (1 GPU), reported in ms")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (profiling captures)")
     ap.add_argument("--f", type=int, default=0, help="override the operand width")
     ap.add_argument("--slab", type=int, default=0)
     ap.add_argument("--blocks", type=int, default=0)
     ap.add_argument("--host-chunk", type=int, default=0)
+    ap.add_argument("--form", type=int, default=0, help="0 register form (default), 1 bulk-copy form")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
@@ -177,8 +181,72 @@ def cpu_reference(c, x, seconds, threads=None):
     return el / it, it, threads
 
 
+def gcn_task(args):
+    """Forward + backward of the workload's GCN stack (widths from the configuration, ReLU between
+    layers, loss = sum of outputs) on one GPU; prints one JSON line with ms per step and the split
+    between CBM products and everything else."""
+    import torch
+    from cbm4gnn_b200 import graphs
+    from cbm4gnn_b200.gcn import GCNModel
+    cfg = graphs.CONFIGS[args.workload]
+    widths = cfg.get("widths", (cfg["f"], 256, 64))
+    c, x, info = make_workload(args, 1)
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    model = GCNModel(widths, structure=c, alpha=cfg["alpha"]).to(dev)
+    xd = torch.from_numpy(x).to(dev).requires_grad_(True)
+    ei = torch.zeros((2, 1), dtype=torch.int64)  # the shared structure is already cached in every layer
+    train = len(widths) == 3
+
+    def step():
+        if train:
+            model.zero_grad(set_to_none=True)
+            xd.grad = None
+            model(xd, ei).sum().backward()
+        else:
+            with torch.no_grad():
+                model(xd, ei)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    c.plan(0).status()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    # the CBM products alone, same operand widths (forward, and backward when training)
+    plan, L = c.plan(0), None
+    from cbm4gnn_b200 import _lib
+    L = _lib.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    prod_ms = 0.0
+    for f in list(widths[1:]) * (2 if train else 1):
+        a = torch.randn((c.num_rows, f), device=dev)
+        b = torch.empty_like(a)
+        for _ in range(3):
+            _lib.check(L.cbm_b200_fused_spmm_update(plan.handle, a.data_ptr(), f, b.data_ptr(), f, f, st))
+        e0.record()
+        for _ in range(10):
+            _lib.check(L.cbm_b200_fused_spmm_update(plan.handle, a.data_ptr(), f, b.data_ptr(), f, f, st))
+        e1.record()
+        torch.cuda.synchronize()
+        prod_ms += e0.elapsed_time(e1) / 10
+    print(json.dumps(dict(metric="gcn_%dlayer_%s_ms" % (len(widths) - 1, "fwd_bwd" if train else "fwd"), value=ms,
+                          unit="ms", n_gpus=1, steps=args.steps, warmup=max(3, args.warmup), ms_per_step=ms,
+                          higher_is_better=False, dtype="f32", data="synthetic",
+                          config=dict(info, widths=list(widths)), cbm_products_ms=prod_ms,
+                          other_ms=ms - prod_ms)))
+    return 0
+
+
 def main():
     args = parse()
+    if args.task == "gcn":
+        return gcn_task(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -227,7 +295,7 @@ def main():
         plan = c.plan(local_rank)
         x_host = torch.from_numpy(x).pin_memory()
         n_out = c.num_rows
-    plan.tune(args.slab, args.blocks, args.host_chunk)
+    plan.tune(args.slab, args.blocks, args.host_chunk, args.form)
     xd = x_host.to(dev, non_blocking=True)
     yd = torch.zeros((n_out, f), device=dev)
     y_host = torch.empty((n_out, f)).pin_memory()

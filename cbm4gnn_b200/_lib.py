@@ -124,7 +124,7 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_plan_destroy", None, c_void_p)
     sig("cbm_b200_plan_info", c_int32, c_void_p, i32p, POINTER(c_int64), i32p, i32p,
         POINTER(c_int64))
-    sig("cbm_b200_plan_tune", c_int32, c_void_p, c_int32, c_int32, c_int32)
+    sig("cbm_b200_plan_tune", c_int32, c_void_p, c_int32, c_int32, c_int32, c_int32)
     sig("cbm_b200_plan_status", c_int32, c_void_p, c_void_p)
     for name in ("cbm_b200_spmm_update", "cbm_b200_fused_spmm_update", "cbm_b200_delta_spmm"):
         sig(name, c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p)

@@ -72,8 +72,8 @@ class _Plan:
         self.n_rows, self.n_delta = n_rows.value, n_delta.value
         self.n_root_children, self.depth, self.device_bytes = n_rc.value, depth.value, nbytes.value
 
-    def tune(self, slab_width=0, n_blocks=0, host_chunk=0):
-        _lib.check(_lib.lib().cbm_b200_plan_tune(self.handle, slab_width, n_blocks, host_chunk))
+    def tune(self, slab_width=0, n_blocks=0, host_chunk=0, form=0):
+        _lib.check(_lib.lib().cbm_b200_plan_tune(self.handle, slab_width, n_blocks, host_chunk, form))
 
     def status(self, stream=0):
         _lib.check(_lib.lib().cbm_b200_plan_status(self.handle, ctypes.c_void_p(stream)))

@@ -105,17 +105,19 @@ struct Candidates {
 // The reference tests every pair of rows that share a column (the non-zeros of A*A^T,
 // cbm/cbm_extensions.cpp:87-102).  The same set of candidate edges is produced here without
 // visiting all those pairs: an edge u -> v passes the rule  h(u,v) < |v| - alpha  exactly when
-// |u ∩ v| > (|u| + alpha) / 2, i.e. when at least t(u) = floor((|u| + alpha) / 2) + 1 of u's columns
-// are also in v.  Order all columns from rarest to most frequent; if u and v share t(u) columns,
-// one of them must be among u's first |u| - t(u) + 1 columns in that order (only t(u) - 1 columns
-// lie behind them).  So it is enough to look, for every possible parent u, at the rows that hold
-// one of those few rare columns, and to count the intersection exactly for each of them.  Hub
-// columns, which make A*A^T explode, almost never fall in that prefix.
+// |u ∩ v| > (|u| + alpha) / 2, i.e. when at least t = floor((|u| + alpha) / 2) + 1 of u's columns
+// are also in v.  Order all columns from rarest to most frequent.  If u and v share t columns,
+// then for any j <= t at least j of them lie among u's first |u| - t + j columns in that order
+// (only t - j columns lie behind them).  So for every possible parent u the rows holding its rare
+// columns are counted through the column lists — hub columns, which make A*A^T explode, almost
+// never fall in that prefix — and only rows reaching j hits get their intersection with u counted
+// exactly.
 Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
     const i32 n = a.n;
     struct Tri {
         i32 src, dst, w;
     };
+    const i32 J = 8;  // hits demanded inside the prefix
     // rank of every column in the rare-to-frequent order (ties by id)
     std::vector<i32> by_freq((size_t)n);
     for (i32 c = 0; c < n; ++c) by_freq[c] = c;
@@ -133,9 +135,9 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
 
 #pragma omp parallel
     {
-        std::vector<i32> in_u((size_t)n, -1);   // column -> u if the column is in row u
-        std::vector<i32> seen((size_t)n, -1);   // row -> u if already listed as a candidate of u
-        std::vector<i32> cand, cols;
+        std::vector<i32> in_u((size_t)n, -1);  // column -> u if the column is in row u
+        std::vector<i32> hits((size_t)n, 0);   // row -> shared columns seen inside u's prefix
+        std::vector<i32> touched, cols;
 #pragma omp for schedule(dynamic, 1)
         for (i32 b = 0; b < n_blocks; ++b) {
             std::vector<Tri>& out = found[b];
@@ -149,37 +151,44 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
                 const i64 need64 = std::max<i64>(half_floor + 1, 1);
                 if (need64 > nu) continue;  // no row can contain that many of u's columns
                 const i32 need = (i32)need64;
+                const i32 j_hits = std::min(J, need);
+                const i32 plen = nu - need + j_hits;
                 const i32* ub = a.idx.data() + a.ptr[u];
                 const i32* ue = a.idx.data() + a.ptr[u + 1];
                 cols.assign(ub, ue);
-                const i32 plen = nu - need + 1;
                 if (plen < nu)
                     std::partial_sort(cols.begin(), cols.begin() + plen, cols.end(),
                                       [&](i32 x, i32 y) { return rank[x] < rank[y]; });
-                for (const i32* k = ub; k != ue; ++k) in_u[*k] = u;
-                cand.clear();
-                seen[u] = u;
+                touched.clear();
                 for (i32 i = 0; i < plen; ++i) {
                     const i32 colk = cols[i];
                     for (i64 q = at.ptr[colk]; q < at.ptr[colk + 1]; ++q) {
                         const i32 v = at.idx[q];
-                        if (seen[v] != u) {
-                            seen[v] = u;
-                            cand.push_back(v);
-                        }
+                        if (hits[v]++ == 0) touched.push_back(v);
                     }
                 }
-                std::sort(cand.begin(), cand.end());
-                for (i32 v : cand) {
+                bool marked = false;
+                std::sort(touched.begin(), touched.end());
+                for (i32 v : touched) {
+                    const i32 in_prefix = hits[v];
+                    hits[v] = 0;
+                    if (v == u || in_prefix < j_hits) continue;
                     const i32 nv = a.len(v);
                     if (nv < need) continue;
-                    const i32* vb = a.idx.data() + a.ptr[v];
-                    const i32* ve = a.idx.data() + a.ptr[v + 1];
-                    i32 both = 0;
-                    if ((i64)nv <= (i64)16 * nu) {
-                        for (const i32* k = vb; k != ve; ++k) both += (in_u[*k] == u);
-                    } else {
-                        for (const i32* k = ub; k != ue; ++k) both += std::binary_search(vb, ve, *k);
+                    i32 both = in_prefix;
+                    if (plen < nu) {  // the frequent tail of u still has to be looked at
+                        const i32* vb = a.idx.data() + a.ptr[v];
+                        const i32* ve = a.idx.data() + a.ptr[v + 1];
+                        if ((i64)nv <= (i64)12 * (nu - plen)) {
+                            if (!marked) {
+                                for (const i32* k = ub; k != ue; ++k) in_u[*k] = u;
+                                marked = true;
+                            }
+                            both = 0;
+                            for (const i32* k = vb; k != ve; ++k) both += (in_u[*k] == u);
+                        } else {
+                            for (i32 i = plen; i < nu; ++i) both += std::binary_search(vb, ve, cols[i]);
+                        }
                     }
                     const i32 h = nu + nv - 2 * both;
                     if (h < nv - alpha) out.push_back({u, v, h});  // cbm/cbm_extensions.cpp:93-101

@@ -54,19 +54,29 @@ using u64 = unsigned long long;
     } while (0)
 
 // One work item of the schedule, in processing order.  32 bytes, read as two 16-byte loads.
+//
 // A row with many delta entries is cut into segments: all but the last become PARTIAL items that
-// leave their share of the gather in a scratch slot; the last item of the row (placed directly
-// after them) adds those slots to its own share and finishes the row.
+// leave their share of the gather in a scratch slot (slot index = the item's own position); the
+// last segment is the row's finishing item, which adds those slots to its own share.
+//
+// The schedule has two parts.  Positions [0, n_prefix) hold the items that wait for nobody — first
+// every PARTIAL item, then the unsplit children of the virtual root, longest first.  Positions
+// [n_prefix, n_items) hold the items that may wait: finishing items of split rows and every row
+// below the first level, in breadth-first order, so that whatever an item waits for has a smaller
+// position.  Delta entries are stored in item order, hence consecutive items own consecutive
+// entry ranges.
 struct __align__(16) RowDesc {
-    i32 out_row;      // row of y this item produces (local to the shard); scratch slot if PARTIAL
+    i32 out_row;      // row of y this item produces (local to the shard); unused if PARTIAL
     i32 parent_row;   // row of y holding the parent's finished row, -1 under the virtual root
     i32 parent_pos;   // parent's position in processing order (index of its ready flag)
-    i32 flags;        // UNIT_* bits; bits 8.. = number of PARTIAL items directly before this one
-    i32 beg, end;     // delta entries of the item in the plan's col/val arrays
+    i32 info;         // bits 0-1 ITEM_* flags, bits 8-15 number of delta entries (<= 255),
+                      // bits 16-31 number of PARTIAL items of this row (finishing items only)
+    i32 beg;          // first delta entry of the item in the plan's col/val arrays
+    i32 first_part;   // position of the row's first PARTIAL item (when there are any)
     float scale;      // s_v  = D^-1/2 of this row (1 when the plan has no multiplier)
     float inv_parent; // 1/s_u of the parent (1 when none)
 };
-enum : int { UNIT_PUBLISH = 1, UNIT_PARTIAL = 2, UNIT_NPART_SHIFT = 8 };
+enum : int { ITEM_PUBLISH = 1, ITEM_PARTIAL = 2, ITEM_LEN_SHIFT = 8, ITEM_NPART_SHIFT = 16 };
 
 enum Mode : int { MODE_FUSED = 0, MODE_DELTA_ONLY = 1, MODE_UPDATE_ONLY = 2 };
 
@@ -78,16 +88,20 @@ struct KParams {
     float* y;
     i64 ldx, ldy;
     i32 f;
-    i32 slab_w;     // columns per slab
-    i32 n_items;    // work items per slab (rows + extra segments of long rows)
-    i64 n_units;    // n_items * n_slabs
-    float* scratch; // n_slabs * n_slots * slab_w floats: partial sums of long rows
-    i32 n_slots;
-    u64* counter;   // [0] next chunk to claim, [1] warps that have left; both 0 between launches
-    u64 n_warps;    // warps in this launch
-    i32* flags;     // n_slabs * n_items ready flags holding the epoch of the launch that set them
+    i32 slab_w;      // columns per slab
+    i32 n_items;     // work items per slab
+    i32 n_prefix;    // items that never wait (claimed `group` at a time)
+    i32 group;       // prefix items per claim
+    i32 n_pclaims;   // ceil(n_prefix / group)
+    i32 claims_per_slab;  // n_pclaims + (n_items - n_prefix)
+    i64 n_claims;    // claims_per_slab * n_slabs
+    float* scratch;  // n_slabs * n_partial * slab_w floats: partial sums of long rows
+    i32 n_partial;   // PARTIAL items (positions [0, n_partial))
+    u64* counter;    // [0] next claim, [1] warps that have left; both 0 between launches
+    u64 n_warps;     // warps in this launch
+    i32* flags;      // n_slabs * n_items ready flags holding the epoch of the launch that set them
     i32 epoch;
-    i32* status;    // 0 ok; non-zero: a wait gave up
+    i32* status;     // 0 ok; non-zero: a wait gave up
     i32 mode;
     i32 use_scale;
     u64 wait_ns;
@@ -190,18 +204,6 @@ struct Vec<false> {
     static __device__ __forceinline__ T mul(float w, T a) { return w * a; }
 };
 
-// A warp signs off; the last one out rewinds both counters for the next launch.  This holds on
-// the drain path after a failed wait too, so a plan stays usable after a timeout.
-__device__ __forceinline__ void leave(const KParams& p, int lane) {
-    if (lane == 0) {
-        if (atomicAdd(p.counter + 1, 1ULL) == p.n_warps - 1) {
-            p.counter[0] = 0;
-            p.counter[1] = 0;
-            __threadfence();
-        }
-    }
-}
-
 // acc[v] += sum over entries [beg,end) of val * X[col, slab columns of this lane].
 // The 32 lanes fetch 32 (col, val) pairs at once and pass them round by shuffle.  Row fetches are
 // issued UNROLL at a time so that several independent loads per lane are in flight; the weights
@@ -251,11 +253,102 @@ __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
     }
 }
 
-// The fused product kernel.  One warp per (row segment, column slab) item; NV vectors per lane.
+// A warp signs off; the last one out rewinds both counters for the next launch.  This holds on
+// the drain path after a failed wait too, so a plan stays usable after a timeout.
+__device__ __forceinline__ void leave(const KParams& p, int lane) {
+    if (lane == 0) {
+        if (atomicAdd(p.counter + 1, 1ULL) == p.n_warps - 1) {
+            p.counter[0] = 0;
+            p.counter[1] = 0;
+            __threadfence();
+        }
+    }
+}
+
+// Maps a claim number to (slab, first item, item count): inside a slab the prefix is handed out
+// `group` items at a time, the rest one item at a time.  Only items that never wait are grouped:
+// a warp that sits on an item waiting for a neighbour would starve the items behind it in its
+// group, which others in turn wait for (measured: 16x slower with 4 mixed items per claim).
+__device__ __forceinline__ void decode_claim(const KParams& p, u64 t, i32& slab, i32& first, i32& count) {
+    const unsigned u = (unsigned)t;  // the host refuses launches of 2^31 claims or more
+    slab = (i32)(u / (unsigned)p.claims_per_slab);
+    const i32 r = (i32)(u - (unsigned)slab * (unsigned)p.claims_per_slab);
+    if (r < p.n_pclaims) {
+        first = r * p.group;
+        count = min(p.group, p.n_prefix - first);
+    } else {
+        first = p.n_prefix + (r - p.n_pclaims);
+        count = 1;
+    }
+}
+
+// Everything that happens to an item once its own gather is in `acc`: park a PARTIAL share, or
+// collect the row's parked shares, add the parent's finished row, scale, store and publish.
+// Returns false when a bounded wait ran out.
+template <int NV, bool V4>
+__device__ __forceinline__ bool finish_item(const KParams& p, i32 slab, i32 pos, i32 out_row,
+                                            i32 parent_row, i32 parent_pos, i32 info,
+                                            i32 first_part, float scale, float inv_parent,
+                                            typename Vec<V4>::T (&acc)[NV], const bool (&ok)[NV],
+                                            i32 c0, int lane) {
+    using V = Vec<V4>;
+    constexpr int STEP = 32 * V::E;
+    i32* slab_flags = p.flags + (i64)slab * p.n_items;
+    if (info & ITEM_PARTIAL) {
+        float* slot = p.scratch + ((i64)slab * p.n_partial + pos) * p.slab_w + lane * V::E;
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+            if (ok[v]) V::st(slot + v * STEP, acc[v]);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release(slab_flags + pos, p.epoch);
+        return true;
+    }
+    const i32 n_part = (i32)((unsigned)info >> ITEM_NPART_SHIFT);
+    if (n_part > 0 && p.mode != MODE_UPDATE_ONLY) {
+        for (i32 k = 0; k < n_part; ++k) {
+            if (!wait_ready(slab_flags + first_part + k, p.epoch, p.status, p.wait_ns)) return false;
+            const float* slot =
+                p.scratch + ((i64)slab * p.n_partial + first_part + k) * p.slab_w + lane * V::E;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if (ok[v]) acc[v] = V::fma(1.0f, V::ld_l2(slot + v * STEP), acc[v]);
+        }
+    }
+    const i32 lane_col = c0 + lane * V::E;
+    if (p.mode != MODE_DELTA_ONLY) {
+        if (parent_row >= 0) {
+            if (!wait_ready(slab_flags + parent_pos, p.epoch, p.status, p.wait_ns)) return false;
+            const float* prow = p.y + (i64)parent_row * p.ldy + lane_col;
+            const float ip = p.use_scale ? inv_parent : 1.0f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if (ok[v]) acc[v] = V::fma(ip, V::ld_l2(prow + v * STEP), acc[v]);
+        }
+        if (p.use_scale) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) acc[v] = V::mul(scale, acc[v]);
+        }
+    }
+    float* yrow = p.y + (i64)out_row * p.ldy + lane_col;
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+        if (ok[v]) V::st(yrow + v * STEP, acc[v]);
+    if ((info & ITEM_PUBLISH) && p.mode != MODE_DELTA_ONLY) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release(slab_flags + pos, p.epoch);
+    }
+    return true;
+}
+
+// Product kernel, register form: one warp per (item, column slab), the gather held in registers.
+// Serves operands the bulk-copy form cannot take (width not a multiple of 4 floats, unaligned
+// pointers) and the update-only mode, which gathers nothing.  Launched with group = 1.
 // UNROLL = row fetches in flight per lane, MINB = thread blocks the register budget must allow
 // per SM.
 template <int NV, bool V4, int UNROLL, int MINB>
-__global__ void __launch_bounds__(256, MINB) cbm_rows_kernel(const KParams p) {
+__global__ void __launch_bounds__(256, MINB) cbm_items_kernel(const KParams p) {
     using V = Vec<V4>;
     using T = typename V::T;
     constexpr int STEP = 32 * V::E;
@@ -264,95 +357,262 @@ __global__ void __launch_bounds__(256, MINB) cbm_rows_kernel(const KParams p) {
         u64 t = 0;
         if (lane == 0) t = atomicAdd(p.counter, 1ULL);
         t = __shfl_sync(0xffffffffu, t, 0);
-        if (t >= (u64)p.n_units) {
+        if (t >= (u64)p.n_claims) {
             leave(p, lane);
             return;
         }
-        // One item per claim.  Handing a warp several consecutive items makes it sit on an item
-        // that waits for a neighbour while the items behind it (which others wait for) starve.
-        {
-            const unsigned u = (unsigned)t;  // the host refuses launches of 2^31 items or more
-            const i32 slab = (i32)(u / (unsigned)p.n_items);
-            const i32 pos = (i32)(u - (unsigned)slab * (unsigned)p.n_items);
+        i32 slab, first, count;
+        decode_claim(p, t, slab, first, count);
+        const i32 c0 = slab * p.slab_w;
+        const i32 wcols = min(p.slab_w, p.f - c0);
+        bool ok[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) ok[v] = (lane * V::E + v * STEP) < wcols;
+        for (i32 pos = first; pos < first + count; ++pos) {
             const int4 da = __ldg((const int4*)(p.desc + pos));
             const int4 db = __ldg((const int4*)(p.desc + pos) + 1);
-            const i32 out_row = da.x, parent_row = da.y, parent_pos = da.z, flags = da.w;
-            const i32 beg = db.x, end = db.y;
-            const float scale = __int_as_float(db.z), inv_parent = __int_as_float(db.w);
-            const bool partial = (flags & UNIT_PARTIAL) != 0;
-            if (partial && p.mode == MODE_UPDATE_ONLY) continue;
-            const i32 c0 = slab * p.slab_w;
-            const i32 wcols = min(p.slab_w, p.f - c0);
-            const i32 lane_col = c0 + lane * V::E;
-            bool ok[NV];
-#pragma unroll
-            for (int v = 0; v < NV; ++v) ok[v] = (lane * V::E + v * STEP) < wcols;
-            i32* my_flag = p.flags + (i64)slab * p.n_items + pos;
+            const i32 info = da.w;
+            if ((info & ITEM_PARTIAL) && p.mode == MODE_UPDATE_ONLY) continue;  // nothing to gather
             T acc[NV];
-            float* yrow = p.y + (i64)out_row * p.ldy + lane_col;
             if (p.mode == MODE_UPDATE_ONLY) {
+                const float* yrow = p.y + (i64)da.x * p.ldy + c0 + lane * V::E;
 #pragma unroll
                 for (int v = 0; v < NV; ++v) acc[v] = ok[v] ? V::ld_l2(yrow + v * STEP) : V::zero();
             } else {
 #pragma unroll
                 for (int v = 0; v < NV; ++v) acc[v] = V::zero();
-                gather_row<NV, V4, UNROLL>(p.col, p.val, beg, end, p.x + lane_col, p.ldx, ok, acc, lane);
+                const i32 len = (info >> ITEM_LEN_SHIFT) & 0xff;
+                gather_row<NV, V4, UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0 + lane * V::E, p.ldx,
+                                           ok, acc, lane);
             }
-            if (partial) {
-                float* slot = p.scratch + ((i64)slab * p.n_slots + out_row) * p.slab_w + lane * V::E;
-#pragma unroll
-                for (int v = 0; v < NV; ++v)
-                    if (ok[v]) V::st(slot + v * STEP, acc[v]);
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) st_release(my_flag, p.epoch);
-                continue;
-            }
-            const i32 n_part = flags >> UNIT_NPART_SHIFT;
-            if (n_part > 0 && p.mode != MODE_UPDATE_ONLY) {
-                const i32 last_slot = __ldg(&p.desc[pos - 1].out_row);
-                for (i32 k = 0; k < n_part; ++k) {
-                    if (!wait_ready(my_flag - n_part + k, p.epoch, p.status, p.wait_ns)) {
-                        leave(p, lane);
-                        return;
-                    }
-                    const float* slot = p.scratch +
-                                        ((i64)slab * p.n_slots + (last_slot - (n_part - 1) + k)) * p.slab_w +
-                                        lane * V::E;
-#pragma unroll
-                    for (int v = 0; v < NV; ++v)
-                        if (ok[v]) acc[v] = V::fma(1.0f, V::ld_l2(slot + v * STEP), acc[v]);
-                }
-            }
-            if (p.mode != MODE_DELTA_ONLY) {
-                if (parent_row >= 0) {
-                    if (!wait_ready(p.flags + (i64)slab * p.n_items + parent_pos, p.epoch, p.status,
-                                    p.wait_ns)) {
-                        leave(p, lane);
-                        return;
-                    }
-                    const float* prow = p.y + (i64)parent_row * p.ldy + lane_col;
-                    const float ip = p.use_scale ? inv_parent : 1.0f;
-#pragma unroll
-                    for (int v = 0; v < NV; ++v)
-                        if (ok[v]) acc[v] = V::fma(ip, V::ld_l2(prow + v * STEP), acc[v]);
-                }
-                if (p.use_scale) {
-#pragma unroll
-                    for (int v = 0; v < NV; ++v) acc[v] = V::mul(scale, acc[v]);
-                }
-            }
-#pragma unroll
-            for (int v = 0; v < NV; ++v)
-                if (ok[v]) V::st(yrow + v * STEP, acc[v]);
-            if ((flags & UNIT_PUBLISH) && p.mode != MODE_DELTA_ONLY) {
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) st_release(my_flag, p.epoch);
+            if (!finish_item<NV, V4>(p, slab, pos, da.x, da.y, da.z, info, db.y, __int_as_float(db.z),
+                                     __int_as_float(db.w), acc, ok, c0, lane)) {
+                leave(p, lane);
+                return;
             }
         }
     }
 }
+
+// ------------------------------------------------------------------------------------------
+// Bulk-copy form of the product kernel.
+//
+// The register form keeps at most UNROLL row fetches per lane in flight, so a typical row of 20-30
+// delta entries costs several memory round trips in a row, on top of the round trips for the
+// claim, the descriptor and the indices.  Here each lane issues ONE bulk asynchronous copy
+// (cp.async.bulk, the untiled TMA path) that brings a whole slab-wide piece of one operand row
+// into shared memory, so up to NB rows per stage are in flight per warp and complete on an
+// mbarrier; stages alternate so the next batch is on its way while the current one is summed out
+// of shared memory.  Items of the never-waiting prefix are claimed `group` at a time and their
+// consecutive entry ranges are streamed as one sequence of batches, which amortises the claim and
+// keeps short rows from leaving the pipeline empty.
+//
+// Measured on B200 (100 000-row product, F = 500): the copy engine retires about 7 G bulk copies
+// per second whatever their size between 512 B and 1 KB, so 512-byte pieces reach 3.5 TB/s and
+// 1 KB pieces 7 TB/s, against 12.8 TB/s for the register form.  Row pieces of a few hundred bytes
+// are too small for this path; it is kept as an opt-in form (cbm_b200_plan_tune, form = 1) and the
+// register form is the default.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_addr(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded: gives up after two seconds (each poll itself blocks for a hardware-defined slice).
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, i32* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const u64 t0 = global_ns();
+    for (unsigned spins = 0; spins < (1u << 24); ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 63u) == 63u && global_ns() - t0 > 2000000000ULL) break;
+    }
+    atomicExch(status, CBM_B200_ERR_TIMEOUT);
+    return false;
+}
+// One row piece global -> shared; src, dst and bytes are multiples of 16 (the host checks).
+__device__ __forceinline__ void bulk_copy_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+template <int SLABW, int NB, int STAGES>
+struct TmaLayout {
+    static constexpr int SLABB = SLABW * 4;                   // bytes of one row piece
+    static constexpr int STAGE_BYTES = NB * SLABB;            // NB row pieces
+    // rounded up so that every warp's area starts 128-byte aligned (bulk copies need 16)
+    static constexpr int WARP_BYTES = (STAGES * STAGE_BYTES + STAGES * NB * 4 + STAGES * 8 + 127) / 128 * 128;
+    static __host__ __device__ constexpr int smem_bytes(int warps) { return warps * WARP_BYTES; }
+};
+
+template <int SLABW, int NB, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) cbm_items_tma_kernel(const KParams p) {
+    using V = Vec<true>;
+    using T = float4;
+    using L = TmaLayout<SLABW, NB, STAGES>;
+    constexpr int NV = SLABW / 128;
+    constexpr int STEP = 128;
+    static_assert(NB <= 32 && SLABW % 128 == 0, "one lane per staged row; slabs of 128 floats");
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    unsigned char* my = smem + (size_t)warp * L::WARP_BYTES;
+    unsigned char* rows = my;                                               // [STAGES][NB][SLABB]
+    float* wts = reinterpret_cast<float*>(my + STAGES * L::STAGE_BYTES);    // [STAGES][NB]
+    const unsigned bar0 = smem_addr(my + STAGES * L::STAGE_BYTES + STAGES * NB * 4);
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_async_proxy();
+    __syncwarp();
+    unsigned parity = 0;  // bit s = phase the next wait on stage s looks for
+
+    for (;;) {
+        u64 t = 0;
+        if (lane == 0) t = atomicAdd(p.counter, 1ULL);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t >= (u64)p.n_claims) {
+            leave(p, lane);
+            return;
+        }
+        i32 slab, first, count;
+        decode_claim(p, t, slab, first, count);
+        const i32 c0 = slab * SLABW;
+        const i32 wcols = min(SLABW, p.f - c0);
+        const unsigned piece = (unsigned)wcols * 4u;
+        bool ok[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) ok[v] = (lane * 4 + v * STEP) < wcols;
+
+        // lane i keeps the descriptor of item first + i
+        int4 da = make_int4(0, -1, -1, 0), db = make_int4(0, 0, 0, 0);
+        if (lane < count) {
+            da = __ldg((const int4*)(p.desc + first + lane));
+            db = __ldg((const int4*)(p.desc + first + lane) + 1);
+        }
+        const i32 my_end = db.x + ((da.w >> ITEM_LEN_SHIFT) & 0xff);
+        const i32 e_begin = __shfl_sync(0xffffffffu, db.x, 0);
+        const i32 e_end = __shfl_sync(0xffffffffu, my_end, count - 1);
+        const i32 n_batches = (e_end - e_begin + NB - 1) / NB;
+        const float* xs = p.x + c0;
+
+        // indices of batch q, one entry per lane
+        auto load_idx = [&](i32 q, i32& c, float& w) {
+            const i32 e = e_begin + q * NB + lane;
+            c = -1;
+            w = 0.f;
+            if (lane < NB && e < e_end) {
+                c = __ldg(p.col + e);
+                w = __ldg(p.val + e);
+            }
+        };
+        // start the copies of batch q into its stage
+        auto issue = [&](i32 q, i32 c, float w) {
+            const int s = q % STAGES;
+            const i32 cnt = min(NB, e_end - (e_begin + q * NB));
+            const unsigned bar = bar0 + 8 * s;
+            __syncwarp();         // every lane has finished reading this stage
+            fence_async_proxy();  // ... before the copies of the async proxy may land in it
+            if (lane == 0) mbar_expect_tx(bar, (unsigned)cnt * piece);
+            if (lane < NB) wts[s * NB + lane] = w;
+            __syncwarp();
+            if (lane < cnt)
+                bulk_copy_g2s(smem_addr(rows + (size_t)s * L::STAGE_BYTES + (size_t)lane * L::SLABB),
+                              xs + (i64)c * p.ldx, piece, bar);
+        };
+
+        T acc[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) acc[v] = V::zero();
+        i32 cur = 0;  // item being accumulated
+        i32 cur_end = __shfl_sync(0xffffffffu, my_end, 0);
+        bool alive = true;
+        auto flush = [&](i32 i) {  // finish item first + i with what is in acc, then clear acc
+            const i32 o = __shfl_sync(0xffffffffu, da.x, i), pr = __shfl_sync(0xffffffffu, da.y, i);
+            const i32 pp = __shfl_sync(0xffffffffu, da.z, i), inf = __shfl_sync(0xffffffffu, da.w, i);
+            const i32 fp = __shfl_sync(0xffffffffu, db.y, i);
+            const float sc = __int_as_float(__shfl_sync(0xffffffffu, db.z, i));
+            const float ip = __int_as_float(__shfl_sync(0xffffffffu, db.w, i));
+            alive = finish_item<NV, true>(p, slab, first + i, o, pr, pp, inf, fp, sc, ip, acc, ok, c0, lane);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) acc[v] = V::zero();
+        };
+
+        i32 c_nx = -1;
+        float w_nx = 0.f;
+        i32 issued = 0;
+        if (n_batches > 0) {
+            load_idx(0, c_nx, w_nx);
+            issue(0, c_nx, w_nx);
+            issued = 1;
+            if (n_batches > 1) load_idx(1, c_nx, w_nx);
+        }
+        for (i32 q = 0; q < n_batches && alive; ++q) {
+            while (issued < n_batches && issued - q < STAGES) {  // keep the other stages busy
+                issue(issued, c_nx, w_nx);
+                ++issued;
+                if (issued < n_batches) load_idx(issued, c_nx, w_nx);
+            }
+            const int s = q % STAGES;
+            if (!mbar_wait(bar0 + 8 * s, (parity >> s) & 1u, p.status)) {
+                alive = false;
+                break;
+            }
+            parity ^= 1u << s;
+            const i32 e0 = e_begin + q * NB;
+            const i32 cnt = min(NB, e_end - e0);
+            const unsigned char* st = rows + (size_t)s * L::STAGE_BYTES + lane * 16;
+            const float* wq = wts + s * NB;
+            for (i32 l = 0; l < cnt && alive; ++l) {
+                while (e0 + l == cur_end && cur < count - 1 && alive) {  // entry belongs to a later item
+                    flush(cur);
+                    ++cur;
+                    cur_end = __shfl_sync(0xffffffffu, my_end, cur);
+                }
+                const float w = wq[l];
+#pragma unroll
+                for (int v = 0; v < NV; ++v)
+                    if (ok[v])
+                        acc[v] = V::fma(w, *reinterpret_cast<const float4*>(st + (size_t)l * L::SLABB + v * 512),
+                                        acc[v]);
+            }
+        }
+        if (!alive) {  // a wait ran out: the status word is set, drain
+            leave(p, lane);
+            return;
+        }
+        while (cur < count && alive) {  // the last item, and any empty items behind it
+            flush(cur);
+            ++cur;
+        }
+        if (!alive) {
+            leave(p, lane);
+            return;
+        }
+    }
+}
+
 // Plain CSR product (no tree): rows in natural order, one warp per (row, slab), grid-stride.
 template <int NV, bool V4>
 __global__ void __launch_bounds__(256)
@@ -426,7 +686,8 @@ struct cbm_b200_plan {
     i32 n_out = 0;     // rows of the output shard (owned label range)
     i32 n_rows = 0;    // rows actually computed
     i32 n_items = 0;   // work items per slab (rows + extra segments of long rows)
-    i32 n_slots = 0;   // scratch slots per slab
+    i32 n_prefix = 0;  // items that never wait
+    i32 n_partial = 0; // PARTIAL items = scratch slots per slab
     float* d_scratch = nullptr;
     i64 scratch_cap = 0;
     i64 n_delta = 0;
@@ -449,6 +710,7 @@ struct cbm_b200_plan {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> events;
     i32 host_chunk = 0;
+    i32 form = 0;      // 0 register form, 1 bulk-copy form
     float* stage_x = nullptr;
     float* stage_y = nullptr;
     i64 stage_x_cap = 0, stage_y_cap = 0;
@@ -572,78 +834,91 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
         return l >= own_begin && l < own_end;
     };
 
-    // ---- schedule ----
-    // Owned rows in breadth-first order, except that the children of the virtual root (which wait
-    // for nobody) are issued longest first so that the heavy rows never form the tail.  Any order
-    // in which a parent precedes its children is valid.
-    std::vector<i32> sched;
-    sched.reserve((size_t)(own_end - own_begin));
+    // ---- schedule (layout described at RowDesc) ----
+    const i32 SEG = 128;         // delta entries per item of a split row
+    const i32 SPLIT_OVER = 192;  // rows longer than this are split
+    auto row_len = [&](i32 v) { return delta_crow[v + 1] - delta_crow[v]; };
+    auto is_split = [&](i32 v) { return row_len(v) > SPLIT_OVER; };
+    std::vector<i32> owned_rows;  // breadth-first
+    owned_rows.reserve((size_t)(own_end - own_begin));
     for (i32 v : order)
-        if (owned(v)) sched.push_back(v);
-    {
-        auto first_deep = std::stable_partition(sched.begin(), sched.end(),
-                                                [&](i32 v) { return parent[v] == n; });
-        std::stable_sort(sched.begin(), first_deep, [&](i32 a, i32 b) {
-            return delta_crow[a + 1] - delta_crow[a] > delta_crow[b + 1] - delta_crow[b];
-        });
-    }
-    const i32 SEG = 128;        // delta entries per work item of a long row
-    const i32 SPLIT_OVER = 192; // rows longer than this are cut into segments
-    std::vector<i32> pos_of((size_t)n, -1);
+        if (owned(v)) {
+            const i32 u = parent[v];
+            if (u != n && !owned(u))
+                return cbm::fail(CBM_B200_ERR_ARG,
+                                 "plan_create: owned range cuts a subtree (parent of an owned row "
+                                 "is not owned)");
+            owned_rows.push_back(v);
+        }
     std::vector<RowDesc> desc;
-    desc.reserve(sched.size());
     std::vector<i32> pcol;
     std::vector<float> pval;
     pcol.reserve((size_t)nd_all);
     pval.reserve((size_t)nd_all);
-    i32 depth = 0, n_root_children = 0, n_slots = 0;
-    for (i32 v : sched) {
-        const i32 u = parent[v];
-        if (u != n && !owned(u))
-            return cbm::fail(CBM_B200_ERR_ARG,
-                             "plan_create: owned range cuts a subtree (parent of an owned row "
-                             "is not owned)");
-        const i32 first = (i32)pcol.size();
-        for (i32 k = delta_crow[v]; k < delta_crow[v + 1]; ++k) {
+    auto append_entries = [&](i32 v, i32 from, i32 to) {  // entries [from, to) of row v
+        const i32 beg = (i32)pcol.size();
+        for (i32 k = delta_crow[v] + from; k < delta_crow[v] + to; ++k) {
             pcol.push_back(label(delta_col[k]));
             pval.push_back(delta_val[k]);
         }
-        const i32 len = (i32)pcol.size() - first;
-        i32 n_part = 0;
-        i32 cursor = first;
-        if (len > SPLIT_OVER) {
-            const i32 n_seg = (len + SEG - 1) / SEG;
-            n_part = n_seg - 1;
-            for (i32 k = 0; k < n_part; ++k) {
-                RowDesc q{};
-                q.out_row = n_slots++;
-                q.parent_row = -1;
-                q.parent_pos = -1;
-                q.flags = UNIT_PARTIAL | UNIT_PUBLISH;
-                q.beg = cursor;
-                q.end = cursor + SEG;
-                q.scale = 1.0f;
-                q.inv_parent = 1.0f;
-                cursor += SEG;
-                desc.push_back(q);
-            }
+        return beg;
+    };
+    // 1. PARTIAL items of every split row
+    std::vector<i32> first_part((size_t)n, -1);
+    for (i32 v : owned_rows) {
+        if (!is_split(v)) continue;
+        const i32 n_part = (row_len(v) + SEG - 1) / SEG - 1;
+        if (n_part > 0xffff)
+            return cbm::fail(CBM_B200_ERR_ARG, "plan_create: a row has more than 8388480 delta entries");
+        first_part[v] = (i32)desc.size();
+        for (i32 k = 0; k < n_part; ++k) {
+            RowDesc q{};
+            q.out_row = 0;
+            q.parent_row = -1;
+            q.parent_pos = -1;
+            q.info = ITEM_PARTIAL | ITEM_PUBLISH | (SEG << ITEM_LEN_SHIFT);
+            q.beg = append_entries(v, k * SEG, (k + 1) * SEG);
+            q.first_part = -1;
+            q.scale = 1.0f;
+            q.inv_parent = 1.0f;
+            desc.push_back(q);
         }
+    }
+    const i32 n_partial = (i32)desc.size();
+    // 2. unsplit children of the virtual root, longest first
+    std::vector<i32> pos_of((size_t)n, -1);
+    i32 depth = 0, n_root_children = 0;
+    auto add_row_item = [&](i32 v) {
+        const i32 u = parent[v];
+        const i32 len = row_len(v);
+        const i32 n_part = is_split(v) ? (len + SEG - 1) / SEG - 1 : 0;
         RowDesc d{};
         d.out_row = label(v) - own_begin;
         d.parent_row = (u == n) ? -1 : label(u) - own_begin;
         d.parent_pos = (u == n) ? -1 : pos_of[u];
-        d.flags = n_part << UNIT_NPART_SHIFT;
-        d.beg = cursor;
-        d.end = (i32)pcol.size();
+        d.beg = append_entries(v, n_part * SEG, len);
+        d.info = ((len - n_part * SEG) << ITEM_LEN_SHIFT) | (n_part << ITEM_NPART_SHIFT);
+        d.first_part = first_part[v];
         d.scale = multiplier ? multiplier[v] : 1.0f;
         d.inv_parent = (multiplier && u != n) ? 1.0f / multiplier[u] : 1.0f;
         pos_of[v] = (i32)desc.size();
-        if (u != n) desc[pos_of[u]].flags |= UNIT_PUBLISH;
+        if (u != n) desc[pos_of[u]].info |= ITEM_PUBLISH;
         else ++n_root_children;
         depth = std::max(depth, level[v]);
         desc.push_back(d);
+    };
+    {
+        std::vector<i32> easy;
+        for (i32 v : owned_rows)
+            if (parent[v] == n && !is_split(v)) easy.push_back(v);
+        std::stable_sort(easy.begin(), easy.end(), [&](i32 a, i32 b) { return row_len(a) > row_len(b); });
+        for (i32 v : easy) add_row_item(v);
     }
-    const i32 n_rows_owned = (i32)sched.size();
+    const i32 n_prefix = (i32)desc.size();
+    // 3. everything that may wait, breadth-first: finishing items of split rows, rows with a parent
+    for (i32 v : owned_rows)
+        if (parent[v] != n || is_split(v)) add_row_item(v);
+    const i32 n_rows_owned = (i32)owned_rows.size();
 
     int n_dev = 0;
     CBM_CUDA(cudaGetDeviceCount(&n_dev));
@@ -660,7 +935,8 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
     p->n_out = own_end - own_begin;
     p->n_rows = n_rows_owned;
     p->n_items = (i32)desc.size();
-    p->n_slots = n_slots;
+    p->n_prefix = n_prefix;
+    p->n_partial = n_partial;
     p->n_delta = (i64)pcol.size();
     p->n_root_children = n_root_children;
     p->depth = depth;
@@ -703,10 +979,11 @@ extern "C" int cbm_b200_plan_info(const cbm_b200_plan* p, int32_t* n_rows, int64
 }
 
 extern "C" int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t n_blocks,
-                                  int32_t host_chunk) {
+                                  int32_t host_chunk, int32_t form) {
     if (!p) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: NULL plan");
-    if (slab_width < 0 || n_blocks < 0 || host_chunk < 0)
-        return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: negative knob");
+    if (slab_width < 0 || n_blocks < 0 || host_chunk < 0 || form < 0 || form > 1)
+        return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: knob out of range");
+    p->form = form;
     if (host_chunk % 4 != 0) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: host_chunk must be a multiple of 4");
     p->slab_width = slab_width;
     p->n_blocks = n_blocks;
@@ -730,15 +1007,6 @@ extern "C" int cbm_b200_plan_status(cbm_b200_plan* p, void* stream) {
 
 namespace {
 
-template <int NV, bool V4>
-int launch_rows(const KParams& kp, int blocks, cudaStream_t s) {
-    // Unroll depth and resident blocks per SM were chosen by measurement on B200: forms that
-    // spill registers lose more than extra resident warps gain.
-    cbm_rows_kernel<NV, V4, (NV == 1 ? 8 : 4), (NV == 1 ? 4 : (NV == 2 ? 3 : 2))><<<blocks, 256, 0, s>>>(kp);
-    CBM_CUDA(cudaGetLastError());
-    return CBM_B200_OK;
-}
-
 int check_dense(const char* who, const void* x, i64 ldx, const void* y, i64 ldy, i32 f) {
     if (f <= 0) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": f must be positive");
     if (!y || ldy < f) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": bad y / ldy");
@@ -747,6 +1015,116 @@ int check_dense(const char* who, const void* x, i64 ldx, const void* y, i64 ldy,
         return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": leading dimension exceeds 2^31-1");
     if (x && x == y) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": x and y alias");
     return CBM_B200_OK;
+}
+
+// How one product is cut into claims and which kernel form runs it.
+struct LaunchCfg {
+    Shape sh{};
+    int tma = 0;       // 0: register form; otherwise the bulk-copy form (variant number)
+    i32 group = 1;     // prefix items per claim
+    i32 n_pclaims = 0, claims_per_slab = 0;
+    i64 n_claims = 0;
+    i64 need_flags = 0;        // int32 words
+    i64 need_scratch = 0;      // floats
+};
+
+int plan_cfg(const cbm_b200_plan* p, const char* who, const float* x, i64 ldx, const float* y, i64 ldy,
+             i32 f, int mode, LaunchCfg& c) {
+    const bool can_v4 = (f % 4 == 0) && (ldy % 4 == 0) && aligned16(y) &&
+                        (mode == MODE_UPDATE_ONLY || ((ldx % 4 == 0) && aligned16(x)));
+    int tma = p->form;
+    if (!can_v4 || mode == MODE_UPDATE_ONLY) tma = 0;
+    c.tma = tma;
+    if (tma) {
+        const i32 slab = 256;  // 1 KB row pieces: the copy engine is bound by copies, not bytes
+        c.sh.v4 = true;
+        c.sh.nv = slab / 128;
+        c.sh.slab_w = slab;
+        c.sh.n_slabs = (f + slab - 1) / slab;
+        c.group = 16;
+    } else {
+        c.sh = pick_shape(f, p->slab_width, can_v4);
+        c.group = 1;
+    }
+    c.n_pclaims = (p->n_prefix + c.group - 1) / c.group;
+    c.claims_per_slab = c.n_pclaims + (p->n_items - p->n_prefix);
+    c.n_claims = (i64)c.claims_per_slab * c.sh.n_slabs;
+    c.need_flags = (i64)c.sh.n_slabs * p->n_items;
+    c.need_scratch = (i64)c.sh.n_slabs * p->n_partial * c.sh.slab_w;
+    if (c.need_flags >= (i64)1 << 31)
+        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": rows x column slabs exceeds 2^31 work items");
+    return CBM_B200_OK;
+}
+
+template <int SLABW, int NB, int STAGES, int WARPS>
+int launch_tma(KParams& kp, int sm_count, cudaStream_t s) {
+    using L = TmaLayout<SLABW, NB, STAGES>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    CBM_CUDA(cudaGetDevice(&dev));
+    auto kern = cbm_items_tma_kernel<SLABW, NB, STAGES, WARPS>;
+    const int smem = L::smem_bytes(WARPS);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        CBM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured[dev] = true;
+    }
+    const int blocks = (int)std::max<i64>(1, std::min<i64>(sm_count, (kp.n_claims + WARPS - 1) / WARPS));
+    kp.n_warps = (u64)blocks * WARPS;
+    kern<<<blocks, WARPS * 32, smem, s>>>(kp);
+    CBM_CUDA(cudaGetLastError());
+    return CBM_B200_OK;
+}
+
+template <int NV, bool V4>
+int launch_regs(KParams& kp, int want_blocks, int sm_count, cudaStream_t s) {
+    int blocks = want_blocks > 0 ? want_blocks : sm_count * 8;
+    blocks = (int)std::max<i64>(1, std::min<i64>(blocks, (kp.n_claims + 7) / 8));
+    kp.n_warps = (u64)blocks * 8;
+    // Unroll depth and resident blocks per SM were chosen by measurement on B200: forms that
+    // spill registers lose more than extra resident warps gain.
+    cbm_items_kernel<NV, V4, (NV == 1 ? 8 : 4), (NV == 1 ? 4 : (NV == 2 ? 3 : 2))><<<blocks, 256, 0, s>>>(kp);
+    CBM_CUDA(cudaGetLastError());
+    return CBM_B200_OK;
+}
+
+// Fills the launch parameters that do not depend on where the scratch lives, and launches.
+int launch_plan(cbm_b200_plan* p, const LaunchCfg& c, const float* x, i64 ldx, float* y, i64 ldy, i32 f,
+                int mode, bool use_scale, u64* counter, i32* flags, float* scratch, i32 epoch,
+                cudaStream_t s) {
+    KParams kp{};
+    kp.desc = p->d_desc;
+    kp.col = p->d_col;
+    kp.val = p->d_val;
+    kp.x = x;
+    kp.y = y;
+    kp.ldx = ldx;
+    kp.ldy = ldy;
+    kp.f = f;
+    kp.slab_w = c.sh.slab_w;
+    kp.n_items = p->n_items;
+    kp.n_prefix = p->n_prefix;
+    kp.group = c.group;
+    kp.n_pclaims = c.n_pclaims;
+    kp.claims_per_slab = c.claims_per_slab;
+    kp.n_claims = c.n_claims;
+    kp.scratch = scratch;
+    kp.n_partial = p->n_partial;
+    kp.counter = counter;
+    kp.flags = flags;
+    kp.epoch = epoch;
+    kp.status = p->d_status;
+    kp.mode = mode;
+    kp.use_scale = use_scale ? 1 : 0;
+    kp.wait_ns = 2000000000ULL;
+    if (c.tma) return launch_tma<256, 16, 2, 7>(kp, p->sm_count, s);
+    if (c.sh.v4) {
+        if (c.sh.nv == 1) return launch_regs<1, true>(kp, p->n_blocks, p->sm_count, s);
+        if (c.sh.nv == 2) return launch_regs<2, true>(kp, p->n_blocks, p->sm_count, s);
+        return launch_regs<4, true>(kp, p->n_blocks, p->sm_count, s);
+    }
+    if (c.sh.nv == 1) return launch_regs<1, false>(kp, p->n_blocks, p->sm_count, s);
+    if (c.sh.nv == 2) return launch_regs<2, false>(kp, p->n_blocks, p->sm_count, s);
+    return launch_regs<4, false>(kp, p->n_blocks, p->sm_count, s);
 }
 
 int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* y, i64 ldy, i32 f,
@@ -761,77 +1139,38 @@ int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* 
                          std::string(who) + ": plan was created without a multiplier");
     if (p->n_rows == 0) return CBM_B200_OK;
     DeviceGuard g(p->device);
+    LaunchCfg c;
+    rc = plan_cfg(p, who, x, ldx, y, ldy, f, mode, c);
+    if (rc) return rc;
 
-    const bool can_v4 = (f % 4 == 0) && (ldy % 4 == 0) && aligned16(y) &&
-                        (mode == MODE_UPDATE_ONLY || ((ldx % 4 == 0) && aligned16(x)));
-    const Shape sh = pick_shape(f, p->slab_width, can_v4);
-
-    const i64 need_flags = (i64)sh.n_slabs * p->n_items;
-    if (need_flags >= (i64)1 << 31)
-        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": rows x column slabs exceeds 2^31 work items");
-    if (need_flags > p->flags_cap) {
+    if (c.need_flags > p->flags_cap) {
         // Growing the flag array: the old one may still be read by a launch in flight.
         CBM_CUDA(cudaStreamSynchronize(s));
         cudaFree(p->d_flags);
         p->d_flags = nullptr;
         p->device_bytes -= p->flags_cap * (i64)sizeof(i32);
         p->flags_cap = 0;
-        CBM_CUDA(cudaMalloc((void**)&p->d_flags, (size_t)need_flags * sizeof(i32)));
-        CBM_CUDA(cudaMemset(p->d_flags, 0, (size_t)need_flags * sizeof(i32)));
-        p->flags_cap = need_flags;
-        p->device_bytes += need_flags * (i64)sizeof(i32);
+        CBM_CUDA(cudaMalloc((void**)&p->d_flags, (size_t)c.need_flags * sizeof(i32)));
+        CBM_CUDA(cudaMemset(p->d_flags, 0, (size_t)c.need_flags * sizeof(i32)));
+        p->flags_cap = c.need_flags;
+        p->device_bytes += c.need_flags * (i64)sizeof(i32);
     }
-    const i64 need_scratch = (i64)sh.n_slabs * p->n_slots * sh.slab_w;
-    if (need_scratch > p->scratch_cap) {
+    if (c.need_scratch > p->scratch_cap) {
         CBM_CUDA(cudaStreamSynchronize(s));
         cudaFree(p->d_scratch);
         p->d_scratch = nullptr;
         p->device_bytes -= p->scratch_cap * (i64)sizeof(float);
         p->scratch_cap = 0;
-        CBM_CUDA(cudaMalloc((void**)&p->d_scratch, (size_t)need_scratch * sizeof(float)));
-        p->scratch_cap = need_scratch;
-        p->device_bytes += need_scratch * (i64)sizeof(float);
+        CBM_CUDA(cudaMalloc((void**)&p->d_scratch, (size_t)c.need_scratch * sizeof(float)));
+        p->scratch_cap = c.need_scratch;
+        p->device_bytes += c.need_scratch * (i64)sizeof(float);
     }
     if (p->epoch == INT32_MAX) {  // epochs exhausted: start over on clean flags
         CBM_CUDA(cudaMemsetAsync(p->d_flags, 0, (size_t)p->flags_cap * sizeof(i32), s));
         p->epoch = 0;
     }
-
-    KParams kp{};
-    kp.desc = p->d_desc;
-    kp.col = p->d_col;
-    kp.val = p->d_val;
-    kp.x = x;
-    kp.y = y;
-    kp.ldx = ldx;
-    kp.ldy = ldy;
-    kp.f = f;
-    kp.slab_w = sh.slab_w;
-    kp.n_items = p->n_items;
-    kp.scratch = p->d_scratch;
-    kp.n_slots = p->n_slots;
-    kp.n_units = need_flags;
-    kp.counter = p->d_counter;
-    kp.flags = p->d_flags;
-    kp.epoch = ++p->epoch;
-    kp.status = p->d_status;
-    kp.mode = mode;
-    kp.use_scale = use_scale ? 1 : 0;
-    kp.wait_ns = 2000000000ULL;
-
-    int blocks = p->n_blocks > 0 ? p->n_blocks : p->sm_count * 8;
-    const i64 max_useful = (kp.n_units + 7) / 8;
-    blocks = (int)std::max<i64>(1, std::min<i64>(blocks, max_useful));
-    kp.n_warps = (u64)blocks * 8;
-
-    if (sh.v4) {
-        if (sh.nv == 1) return launch_rows<1, true>(kp, blocks, s);
-        if (sh.nv == 2) return launch_rows<2, true>(kp, blocks, s);
-        return launch_rows<4, true>(kp, blocks, s);
-    }
-    if (sh.nv == 1) return launch_rows<1, false>(kp, blocks, s);
-    if (sh.nv == 2) return launch_rows<2, false>(kp, blocks, s);
-    return launch_rows<4, false>(kp, blocks, s);
+    return launch_plan(p, c, x, ldx, y, ldy, f, mode, use_scale, p->d_counter, p->d_flags, p->d_scratch,
+                       ++p->epoch, s);
 }
 
 }  // namespace
@@ -1007,15 +1346,13 @@ extern "C" int cbm_b200_spmm_update_static(cbm_b200_plan* p, const float* x, int
         return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": plan was created without a multiplier");
     if (p->n_rows == 0) return CBM_B200_OK;
 
-    const bool can_v4 = (f % 4 == 0) && (ldy % 4 == 0) && aligned16(y) && (ldx % 4 == 0) && aligned16(x);
-    const Shape sh = pick_shape(f, p->slab_width, can_v4);
-    const i64 n_units = (i64)sh.n_slabs * p->n_items;
-    if (n_units >= (i64)1 << 31)
-        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": rows x column slabs exceeds 2^31 work items");
+    LaunchCfg c;
+    rc = plan_cfg(p, who, x, ldx, y, ldy, f, MODE_FUSED, c);
+    if (rc) return rc;
     // layout inside the fixed array: counters | ready flags | partial sums
     const i64 off_flags = 256;
-    const i64 off_slots = off_flags + round_up_256(n_units * (i64)sizeof(i32));
-    const i64 need = off_slots + (i64)sh.n_slabs * p->n_slots * sh.slab_w * (i64)sizeof(float);
+    const i64 off_slots = off_flags + round_up_256(c.need_flags * (i64)sizeof(i32));
+    const i64 need = off_slots + c.need_scratch * (i64)sizeof(float);
     if (need > (i64)CBM_B200_STATIC_SCRATCH_BYTES)
         return cbm::fail(CBM_B200_ERR_ARG,
                          std::string(who) + ": this product needs " + std::to_string(need) +
@@ -1030,38 +1367,9 @@ extern "C" int cbm_b200_spmm_update_static(cbm_b200_plan* p, const float* x, int
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     // counters and flags must start at zero; the partial sums are written before they are read
-    CBM_CUDA(cudaMemsetAsync(base, 0, (size_t)(off_flags + n_units * (i64)sizeof(i32)), s));
-
-    KParams kp{};
-    kp.desc = p->d_desc;
-    kp.col = p->d_col;
-    kp.val = p->d_val;
-    kp.x = x;
-    kp.y = y;
-    kp.ldx = ldx;
-    kp.ldy = ldy;
-    kp.f = f;
-    kp.slab_w = sh.slab_w;
-    kp.n_items = p->n_items;
-    kp.n_units = n_units;
-    kp.scratch = reinterpret_cast<float*>(base + off_slots);
-    kp.n_slots = p->n_slots;
-    kp.counter = reinterpret_cast<u64*>(base);
-    kp.flags = reinterpret_cast<i32*>(base + off_flags);
-    kp.epoch = 1;  // flags were just cleared, so any non-zero mark will do
-    kp.status = p->d_status;
-    kp.mode = MODE_FUSED;
-    kp.use_scale = normalized ? 1 : 0;
-    kp.wait_ns = 2000000000ULL;
-    int blocks = p->n_blocks > 0 ? p->n_blocks : p->sm_count * 8;
-    blocks = (int)std::max<i64>(1, std::min<i64>(blocks, (n_units + 7) / 8));
-    kp.n_warps = (u64)blocks * 8;
-    if (sh.v4) {
-        if (sh.nv == 1) return launch_rows<1, true>(kp, blocks, s);
-        if (sh.nv == 2) return launch_rows<2, true>(kp, blocks, s);
-        return launch_rows<4, true>(kp, blocks, s);
-    }
-    if (sh.nv == 1) return launch_rows<1, false>(kp, blocks, s);
-    if (sh.nv == 2) return launch_rows<2, false>(kp, blocks, s);
-    return launch_rows<4, false>(kp, blocks, s);
+    CBM_CUDA(cudaMemsetAsync(base, 0, (size_t)(off_flags + c.need_flags * (i64)sizeof(i32)), s));
+    // flags were just cleared, so any non-zero mark will do as this launch's epoch
+    return launch_plan(p, c, x, ldx, y, ldy, f, MODE_FUSED, normalized != 0,
+                       reinterpret_cast<u64*>(base), reinterpret_cast<i32*>(base + off_flags),
+                       reinterpret_cast<float*>(base + off_slots), 1, s);
 }

@@ -111,9 +111,12 @@ void cbm_b200_plan_destroy(cbm_b200_plan* p);
 int cbm_b200_plan_info(const cbm_b200_plan* p, int32_t* n_rows, int64_t* n_delta,
                        int32_t* n_root_children, int32_t* depth, int64_t* device_bytes);
 
-/* Tuning knobs (0 keeps the default): column-slab width in floats, thread blocks per launch, and
- * the column-chunk width (a multiple of 4) of the host-buffer pipeline below. */
-int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t n_blocks, int32_t host_chunk);
+/* Tuning knobs (0 keeps the default): column-slab width in floats, thread blocks per launch, the
+ * column-chunk width (a multiple of 4) of the host-buffer pipeline below, and the kernel form
+ * (0 = gather held in registers, the default; 1 = operand rows staged in shared memory by bulk
+ * asynchronous copies, for 16-byte aligned operands whose width is a multiple of 4). */
+int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t n_blocks, int32_t host_chunk,
+                       int32_t form);
 
 /* Waits for `stream`, then reports whether any launch since the last call gave up on a bounded
  * wait (CBM_B200_ERR_TIMEOUT) — in that case the outputs of that launch are invalid. */

@@ -298,3 +298,27 @@ def test_config2_full_size_properties(c2_full):
     want = (sp.diags(s[rows]) @ a[rows] @ sp.diags(s)) @ x.astype(np.float64)
     np.testing.assert_allclose(yx[torch.from_numpy(rows).cuda()].cpu().numpy(), want, **TOL)
     c.plan().status()
+
+
+def test_bulk_copy_form_matches_register_form(c1):
+    """The opt-in kernel form that stages operand rows in shared memory with bulk asynchronous
+    copies performs the same arithmetic in the same order: results must be identical."""
+    ei, c = c1
+    n = c.num_rows
+    p = c.plan()
+    L = _lib.lib()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    try:
+        for f in (500, 256, 64, 4):
+            x = torch.randn((n, f), device="cuda")
+            ya, yb, da_, db_ = (torch.full((n, f), float("nan"), device="cuda") for _ in range(4))
+            p.tune(form=0)
+            _lib.check(L.cbm_b200_spmm_update(p.handle, x.data_ptr(), f, ya.data_ptr(), f, f, st))
+            _lib.check(L.cbm_b200_delta_spmm(p.handle, x.data_ptr(), f, da_.data_ptr(), f, f, st))
+            p.tune(form=1)
+            _lib.check(L.cbm_b200_spmm_update(p.handle, x.data_ptr(), f, yb.data_ptr(), f, f, st))
+            _lib.check(L.cbm_b200_delta_spmm(p.handle, x.data_ptr(), f, db_.data_ptr(), f, f, st))
+            p.status()
+            assert torch.equal(ya, yb) and torch.equal(da_, db_)
+    finally:
+        p.tune(form=0)

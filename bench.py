@@ -54,6 +54,7 @@ def parse():
                          "stacked GCN of the workload (1 GPU), reported in ms")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (profiling captures)")
     ap.add_argument("--f", type=int, default=0, help="override the operand width")
+    ap.add_argument("--alpha", type=int, default=-1, help="override the workload's alpha")
     ap.add_argument("--slab", type=int, default=0)
     ap.add_argument("--blocks", type=int, default=0)
     ap.add_argument("--host-chunk", type=int, default=0)
@@ -77,6 +78,8 @@ def make_workload(args, world):
     from cbm4gnn_b200.cbm import cbm_matrix
     from cbm4gnn_b200.utility import add_self_loops
     cfg = dict(graphs.CONFIGS[args.workload])
+    if args.alpha >= 0:
+        cfg["alpha"] = args.alpha
     t0 = time.time()
     if cfg["kind"] == "copy":
         n = max(64, int(cfg["n"] * args.scale)) * world

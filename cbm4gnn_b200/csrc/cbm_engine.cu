@@ -242,13 +242,22 @@ __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
                 for (int v = 0; v < NV; ++v) acc[v] = V::fma(w, t[k][v], acc[v]);
             }
         }
-        for (; j < n_here; ++j) {
-            const i32 c = __shfl_sync(0xffffffffu, mc, j);
-            const float w = __shfl_sync(0xffffffffu, mw, j);
-            const float* r = xs + (i64)c * ldx;
+        if (j < n_here) {  // the last, shorter batch: same code with the surplus fetches switched off
+            T t[UNROLL][NV];
+            const i32 live = n_here - j;
 #pragma unroll
-            for (int v = 0; v < NV; ++v)
-                if (ok[v]) acc[v] = V::fma(w, V::ld_ro(r + v * STEP), acc[v]);
+            for (int k = 0; k < UNROLL; ++k) {
+                const i32 c = __shfl_sync(0xffffffffu, mc, (j + k) & 31);
+                const float* r = xs + (i64)c * ldx;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) t[k][v] = V::ld_ro_if(r + v * STEP, ok[v] && k < live);
+            }
+#pragma unroll
+            for (int k = 0; k < UNROLL; ++k) {
+                const float w = __shfl_sync(0xffffffffu, mw, (j + k) & 31);  // 0 past the end
+#pragma unroll
+                for (int v = 0; v < NV; ++v) acc[v] = V::fma(k < live ? w : 0.f, t[k][v], acc[v]);
+            }
         }
     }
 }

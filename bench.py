@@ -49,6 +49,8 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="with N > 1: weak = graph grows with N (default), strong = same graph sharded")
     ap.add_argument("--task", default="spmm", choices=["spmm", "gcn"],
                     help="spmm: one CBM product per step (the headline); gcn: forward+backward of the "
                          "stacked GCN of the workload (1 GPU), reported in ms")
@@ -74,6 +76,8 @@ def algorithmic_bytes(n_rows, n_delta, n_root_children, f, normalized=True):
 
 def make_workload(args, world):
     import torch
+    if args.scaling == "strong":
+        world = 1
     from cbm4gnn_b200 import graphs
     from cbm4gnn_b200.cbm import cbm_matrix
     from cbm4gnn_b200.utility import add_self_loops
@@ -193,6 +197,8 @@ def gcn_task(args):
     from cbm4gnn_b200.gcn import GCNModel
     cfg = graphs.CONFIGS[args.workload]
     widths = cfg.get("widths", (cfg["f"], 256, 64))
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return sharded_gcn_task(args, widths)
     c, x, info = make_workload(args, 1)
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
@@ -243,6 +249,68 @@ def gcn_task(args):
                           higher_is_better=False, dtype="f32", data="synthetic",
                           config=dict(info, widths=list(widths)), cbm_products_ms=prod_ms,
                           other_ms=ms - prod_ms)))
+    return 0
+
+
+def sharded_gcn_task(args, widths):
+    """Forward pass of the workload's GCN stack with the structure sharded over the ranks
+    (one NCCL all-gather per layer); strong scaling: the graph does not grow with N."""
+    import torch
+    import torch.distributed as dist
+    from cbm4gnn_b200.sharding import ShardedCBM, ShardedGCN
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    args.scaling = "strong"
+    c, x, info = make_workload(args, 1)
+    sh = ShardedCBM(c, rank, world, device_index=local_rank)
+    torch.manual_seed(0)
+    model = ShardedGCN(widths, sh).to(dev)
+    xl = sh.to_labels(torch.from_numpy(x).to(dev))
+    for _ in range(max(3, args.warmup)):
+        model(xl, gather_output=False)
+    sh.plan.status()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        model(xl, gather_output=False)
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    # per-layer local products alone
+    per_layer = []
+    for f in widths[1:]:
+        a = torch.randn((sh.part.n_labels, f), device=dev)
+        out = torch.zeros_like(a)
+        for _ in range(3):
+            sh.local_product(a, out)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(10):
+            sh.local_product(a, out)
+        e1.record()
+        torch.cuda.synchronize()
+        t = e0.elapsed_time(e1) / 10
+        ab = algorithmic_bytes(sh.plan.n_rows, sh.plan.n_delta, sh.plan.n_root_children, f)
+        per_layer.append(dict(f=f, ms=t, GBps=ab / t / 1e6))
+    stats = torch.tensor([ms] + [d["ms"] for d in per_layer], dtype=torch.float64, device=dev)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        for d, t in zip(per_layer, stats[1:].tolist()):
+            d["ms_max_over_ranks"] = t
+        print(json.dumps(dict(metric="gcn_%dlayer_fwd_ms" % (len(widths) - 1), value=stats[0].item(), unit="ms",
+                              n_gpus=world, steps=args.steps, warmup=max(3, args.warmup), ms_per_step=stats[0].item(),
+                              higher_is_better=False, scaling="strong", dtype="f32", data="synthetic",
+                              config=dict(info, widths=list(widths), parallelism=f"subtree-sharded x{world}, "
+                                          "one all-gather per layer", shard_rows=sh.part.shard_rows,
+                                          rows_per_gpu=[int(v) for v in sh.part.counts]),
+                              per_layer_local_product=per_layer)))
+    dist.destroy_process_group()
     return 0
 
 
@@ -382,7 +450,7 @@ def main():
         value = ab_total / (ms_per_step * 1e-3) / 1e9
         achieved = ab_local / (launch_ms * 1e-3) / 1e9
         line = dict(metric="cbm_spmm_algorithmic_GBps", value=value, unit="GB/s", n_gpus=world, steps=args.steps,
-                    warmup=max(3, args.warmup), ms_per_step=ms_per_step, higher_is_better=True, scaling="weak",
+                    warmup=max(3, args.warmup), ms_per_step=ms_per_step, higher_is_better=True, scaling=args.scaling,
                     vs_baseline=None, dtype="f32", data="synthetic",
                     config=dict(info, l2="operands (X + Y = %.0f MB) exceed the 126 MB L2; no flush" %
                                 ((xd.numel() + yd.numel()) * 4 / 1e6),
@@ -390,7 +458,7 @@ def main():
                                 rows_per_gpu=plan.n_rows, delta_entries_per_gpu=plan.n_delta),
                     gpu_launches=args.steps,
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
-                                  peak_source=peak_src, traffic=None, kernel="cbm_rows_kernel",
+                                  peak_source=peak_src, traffic=None, kernel="cbm_items_kernel",
                                   algorithmic_bytes_per_launch=ab_local, launch_ms=launch_ms),
                     clocks=clocks)
         if e2e_ms is not None:

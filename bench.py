@@ -94,7 +94,10 @@ def make_workload(args, world):
     if cfg["normalized"]:
         e = add_self_loops(e)
     t1 = time.time()
-    c = cbm_matrix(e.to(torch.int32), torch.ones(e.shape[1]), alpha=cfg["alpha"], normalized=cfg["normalized"])
+    # torchrun pins OMP_NUM_THREADS to 1; the host builder gets its share of the cores explicitly
+    ranks_here = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")))
+    c = cbm_matrix(e.to(torch.int32), torch.ones(e.shape[1]), alpha=cfg["alpha"], normalized=cfg["normalized"],
+                   n_threads=max(1, (os.cpu_count() or 1) // max(1, ranks_here)))
     f = args.f or cfg["f"]
     x = graphs.make_features(args.workload, c.num_rows, f=f)
     info = dict(workload=args.workload, n=c.num_rows, nnz=int(e.shape[1]), f=f, alpha=cfg["alpha"],

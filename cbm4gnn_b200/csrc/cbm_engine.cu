@@ -22,6 +22,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstring>
+#include <cstdlib>
 #include <new>
 #include <string>
 #include <vector>
@@ -262,6 +263,48 @@ __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
     }
 }
 
+// The same sum for slabs of at most 64 columns (128-bit path): a row piece needs only 16 lanes, so
+// the two half-warps fetch two different delta entries at a time and their partial sums are
+// combined with one shuffle at the end.  Every lane ends up holding the total of its column group.
+template <int UNROLL>
+__device__ __forceinline__ void gather_row_half(const i32* __restrict__ col,
+                                                const float* __restrict__ val, i32 beg, i32 end,
+                                                const float* __restrict__ x_slab, i64 ldx, i32 wcols,
+                                                float4& acc, int lane) {
+    using V = Vec<true>;
+    const int li = lane & 15, half = lane >> 4;
+    const bool okh = li * 4 < wcols;
+    const float* xs = x_slab + li * 4;
+    for (i32 b = beg; b < end; b += 32) {
+        const i32 n_here = min(32, end - b);
+        i32 mc = 0;
+        float mw = 0.f;
+        if (lane < n_here) {
+            mc = __ldg(col + b + lane);
+            mw = __ldg(val + b + lane);
+        }
+        for (i32 j = 0; j < n_here; j += 2 * UNROLL) {
+            float4 t[UNROLL];
+#pragma unroll
+            for (int k = 0; k < UNROLL; ++k) {
+                const i32 idx = j + 2 * k + half;
+                const i32 c = __shfl_sync(0xffffffffu, mc, idx & 31);
+                t[k] = V::ld_ro_if(xs + (i64)c * ldx, okh && idx < n_here);
+            }
+#pragma unroll
+            for (int k = 0; k < UNROLL; ++k) {
+                const i32 idx = j + 2 * k + half;
+                const float w = __shfl_sync(0xffffffffu, mw, idx & 31);
+                acc = V::fma(idx < n_here ? w : 0.f, t[k], acc);
+            }
+        }
+    }
+    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16);
+    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
+    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16);
+    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
+}
+
 // A warp signs off; the last one out rewinds both counters for the next launch.  This holds on
 // the drain path after a failed wait too, so a plan stays usable after a timeout.
 __device__ __forceinline__ void leave(const KParams& p, int lane) {
@@ -391,8 +434,16 @@ __global__ void __launch_bounds__(256, MINB) cbm_items_kernel(const KParams p) {
 #pragma unroll
                 for (int v = 0; v < NV; ++v) acc[v] = V::zero();
                 const i32 len = (info >> ITEM_LEN_SHIFT) & 0xff;
-                gather_row<NV, V4, UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0 + lane * V::E, p.ldx,
-                                           ok, acc, lane);
+                if constexpr (V4 && NV == 1) {
+                    if (wcols <= 64)
+                        gather_row_half<UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0, p.ldx, wcols, acc[0], lane);
+                    else
+                        gather_row<NV, V4, UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0 + lane * V::E,
+                                                   p.ldx, ok, acc, lane);
+                } else {
+                    gather_row<NV, V4, UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0 + lane * V::E, p.ldx,
+                                               ok, acc, lane);
+                }
             }
             if (!finish_item<NV, V4>(p, slab, pos, da.x, da.y, da.z, info, db.y, __int_as_float(db.z),
                                      __int_as_float(db.w), acc, ok, c0, lane)) {
@@ -1053,7 +1104,7 @@ int plan_cfg(const cbm_b200_plan* p, const char* who, const float* x, i64 ldx, c
         c.group = 16;
     } else {
         c.sh = pick_shape(f, p->slab_width, can_v4);
-        c.group = 1;
+        c.group = getenv("CBM_GROUP") ? atoi(getenv("CBM_GROUP")) : 1;
     }
     c.n_pclaims = (p->n_prefix + c.group - 1) / c.group;
     c.claims_per_slab = c.n_pclaims + (p->n_items - p->n_prefix);
@@ -1283,7 +1334,7 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
         const i32 c0 = k * chunk;
         const i32 w = std::min(chunk, f - c0);
         CBM_CUDA(cudaMemcpy2DAsync(p->stage_x + c0, pitch, x + c0, pitch, (size_t)w * sizeof(float),
-                                   (size_t)p->n_labels, cudaMemcpyHostToDevice, p->copy_in));
+                                       (size_t)p->n_labels, cudaMemcpyHostToDevice, p->copy_in));
         CBM_CUDA(cudaEventRecord(p->events[2 * k], p->copy_in));
         CBM_CUDA(cudaStreamWaitEvent(s, p->events[2 * k], 0));
         int rc = run_plan(p, "spmm_update_host", p->stage_x + c0, f, p->stage_y + c0, f, w, MODE_FUSED,

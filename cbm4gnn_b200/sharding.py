@@ -176,14 +176,26 @@ class ShardedGCN(torch.nn.Module):
     def __init__(self, widths, sharded: ShardedCBM):
         super().__init__()
         self.sharded = sharded
+        self._cache = {}
         self.lins = torch.nn.ModuleList(torch.nn.Linear(a, b, bias=False) for a, b in zip(widths[:-1], widths[1:]))
         for lin in self.lins:
             torch.nn.init.xavier_uniform_(lin.weight)
 
+    def _work_buffers(self, width: int, like: torch.Tensor):
+        """Two zero-initialised [n_labels, width] buffers per width, reused across calls: padding
+        rows are never written, so they stay zero."""
+        key = (width, like.device, like.dtype)
+        if key not in self._cache:
+            n = self.sharded.part.n_labels
+            self._cache[key] = (torch.zeros((n, width), dtype=like.dtype, device=like.device),
+                                torch.zeros((n, width), dtype=like.dtype, device=like.device))
+        return self._cache[key]
+
     @torch.no_grad()
     def forward(self, x_labels: torch.Tensor, gather_output: bool = True) -> torch.Tensor:
         """``x_labels``: [n_labels, F_in] in label space.  Returns the output in label space
-        (all rows when ``gather_output``, else only this rank's block is meaningful)."""
+        (all rows when ``gather_output``, else only this rank's block is meaningful).  The returned
+        tensor is a view of a buffer that the next call overwrites."""
         import torch.distributed as dist
         sh = self.sharded
         h_local = x_labels[sh.begin:sh.end]
@@ -191,17 +203,18 @@ class ShardedGCN(torch.nn.Module):
         for i, lin in enumerate(self.lins):
             if i:
                 h_local = h_local.relu()
-            z = torch.zeros((sh.part.n_labels, lin.out_features), dtype=x_labels.dtype, device=x_labels.device)
+            f = lin.out_features
+            fp = -(-f // 4) * 4  # widths are padded to a multiple of 4 floats for the 128-bit path
+            z, out = self._work_buffers(fp, x_labels)
             prev = torch.backends.cuda.matmul.allow_tf32
             torch.backends.cuda.matmul.allow_tf32 = False  # full fp32, as the 1e-4 tolerance needs
             try:
-                torch.mm(h_local, lin.weight.t(), out=z[sh.begin:sh.end])
+                torch.mm(h_local[:, :lin.in_features], lin.weight.t(), out=z[sh.begin:sh.end, :f])
             finally:
                 torch.backends.cuda.matmul.allow_tf32 = prev
             if sh.world > 1:
                 dist.all_gather_into_tensor(z, z[sh.begin:sh.end], group=sh.group)
-            out = torch.zeros_like(z)
             h_local = sh.local_product(z, out)
         if gather_output and sh.world > 1:
             dist.all_gather_into_tensor(out, h_local, group=sh.group)
-        return out
+        return out[:, :self.lins[-1].out_features]

@@ -310,7 +310,8 @@ def test_bulk_copy_form_matches_register_form(c1):
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     try:
         for f in (500, 256, 64, 4):
-            x = torch.randn((n, f), device="cuda")
+            # integer-valued operand: every summation order gives the same floats
+            x = torch.randint(-4, 5, (n, f), device="cuda").float()
             ya, yb, da_, db_ = (torch.full((n, f), float("nan"), device="cuda") for _ in range(4))
             p.tune(form=0)
             _lib.check(L.cbm_b200_spmm_update(p.handle, x.data_ptr(), f, ya.data_ptr(), f, f, st))
@@ -322,3 +323,19 @@ def test_bulk_copy_form_matches_register_form(c1):
             assert torch.equal(ya, yb) and torch.equal(da_, db_)
     finally:
         p.tune(form=0)
+
+
+def test_host_operands_pinned_and_pageable_agree(c1):
+    """Page-locked host operands travel through copy kernels, pageable ones through the runtime's
+    copies; both must give the device-resident result exactly."""
+    ei, c = c1
+    n = c.num_rows
+    for f in (500, 130, 64):
+        x = torch.randn((n, f))
+        want = torch.empty((n, f), device="cuda")
+        c.omp_mkl_csr_spmm_update(x.cuda(), want)
+        got_pageable = torch.empty((n, f))
+        c.omp_mkl_csr_spmm_update(x, got_pageable)
+        got_pinned = torch.empty((n, f)).pin_memory()
+        c.omp_mkl_csr_spmm_update(x.pin_memory(), got_pinned)
+        assert torch.equal(got_pageable, want.cpu()) and torch.equal(got_pinned, want.cpu())

@@ -159,9 +159,10 @@ class ClockSampler:
         return out
 
 
-def cpu_reference(c, x, seconds, threads=None):
+def cpu_reference(c, x, seconds, threads=None, steps=None, warmup=1):
     """The reference's CPU path (cbm/cbm.py:271-275) on the host: torch CSR product (MKL) + OpenMP
-    tree update; repeated for about ``seconds`` and averaged after one warm-up."""
+    tree update.  Either exactly ``steps`` products after ``warmup``, or (steps None) repeated for
+    about ``seconds`` after one warm-up; returns seconds per product, products timed, threads."""
     import torch
     from oracle import cbm_oracle as orc
     threads = threads or os.cpu_count()
@@ -179,14 +180,15 @@ def cpu_reference(c, x, seconds, threads=None):
             orc.fused_update(mr, mc, mult, y, parallel=True)
         return y
 
-    once()
+    for _ in range(max(1, warmup)):
+        once()
     t0 = time.perf_counter()
     it = 0
     while True:
         once()
         it += 1
         el = time.perf_counter() - t0
-        if el > seconds or it >= 50:
+        if (steps is not None and it >= steps) or (steps is None and (el > seconds or it >= 50)):
             break
     return el / it, it, threads
 
@@ -332,10 +334,11 @@ def main():
             return 0
         c, x, info = make_workload(args, max(1, args.gpus))
         ab = algorithmic_bytes(c.num_rows, info["n_delta"], info["n_root_children"], info["f"])
-        per, iters, threads = cpu_reference(c, x, max(5.0, args.cpu_seconds * max(1, args.steps) / 50))
+        per, iters, threads = cpu_reference(c, x, 0.0, steps=args.steps, warmup=max(1, args.warmup))
         val = ab / per / 1e9
         line = dict(impl="reference", metric="cbm_spmm_algorithmic_GBps", value=val, unit="GB/s", n_gpus=args.gpus,
-                    steps=iters, warmup=1, ms_per_step=per * 1e3, higher_is_better=True, scaling="weak",
+                    steps=iters, warmup=max(1, args.warmup), ms_per_step=per * 1e3, higher_is_better=True,
+                    scaling=args.scaling,
                     vs_baseline=None, dtype="f32", data="synthetic",
                     config=dict(info, l2="host run"),
                     cpu_baseline=dict(value=val, unit="GB/s", cores=threads, kind="port",

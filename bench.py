@@ -38,7 +38,7 @@ sys.path.insert(0, ROOT)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the product kernel, from the ncu
 # captures summarised under profiles/ (key: workload, operand width, GPUs, scale).
 DRAM_TRAFFIC: dict = {
-    ("c2", 500, 1, 1.0): 2.027e9,  # profiles/cbm_rows_kernel_c2_f500.md
+    ("c2", 500, 1, 1.0): 2.078e9,  # profiles/cbm_items_kernel_c2_f500.md
 }
 
 

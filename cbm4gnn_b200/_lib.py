@@ -50,6 +50,7 @@ EXPORTED = [
     "cbm_b200_csr_spmm",
     "cbm_b200_spmm_update_host",
     "cbm_b200_spmm_update_static",
+    "cbm_b200_selftest_wait",
 ]
 
 
@@ -135,6 +136,7 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_spmm_update_host", c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32)
     sig("cbm_b200_spmm_update_static", c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32,
         c_int32, c_void_p)
+    sig("cbm_b200_selftest_wait", c_int32, c_int32, c_int32, c_void_p)
     _lib = L
     return L
 

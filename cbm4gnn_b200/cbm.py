@@ -370,25 +370,31 @@ class cbm_matrix:
         return _CBMMatmul.apply(x, self)
 
 
+def _product(cbm: "cbm_matrix", x: torch.Tensor) -> torch.Tensor:
+    """``A @ x`` / normalized product into a fresh tensor.  A CUDA operand whose width is not a
+    multiple of 4 floats is first copied into a zero-padded buffer: the 128-bit kernel path on
+    the padded width is faster than the scalar path on the exact width, copy included."""
+    x = x.contiguous()
+    f = x.size(1)
+    run = cbm.seq_mkl_csr_fused_spmm_update if cbm.normalized else cbm.seq_mkl_csr_spmm_update
+    if x.is_cuda and f % 4 != 0 and f > 4:
+        fp = -(-f // 4) * 4
+        xp = torch.zeros((x.size(0), fp), dtype=x.dtype, device=x.device)
+        xp[:, :f] = x
+        yp = torch.empty((cbm.num_rows, fp), dtype=x.dtype, device=x.device)
+        run(xp, yp)
+        return yp[:, :f]
+    y = torch.empty((cbm.num_rows, f), dtype=x.dtype, device=x.device)
+    run(x, y)
+    return y
+
+
 class _CBMMatmul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cbm):
         ctx.cbm = cbm
-        x = x.contiguous()
-        y = torch.empty((cbm.num_rows, x.size(1)), dtype=x.dtype, device=x.device)
-        if cbm.normalized:
-            cbm.seq_mkl_csr_fused_spmm_update(x, y)
-        else:
-            cbm.seq_mkl_csr_spmm_update(x, y)
-        return y
+        return _product(cbm, x)
 
     @staticmethod
     def backward(ctx, gy):
-        t = ctx.cbm.transposed()
-        gy = gy.contiguous()
-        gx = torch.empty_like(gy)
-        if t.normalized:
-            t.seq_mkl_csr_fused_spmm_update(gy, gx)
-        else:
-            t.seq_mkl_csr_spmm_update(gy, gx)
-        return gx, None
+        return _product(ctx.cbm.transposed(), gy), None

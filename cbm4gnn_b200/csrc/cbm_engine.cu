@@ -1351,6 +1351,41 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
 }
 
 // ------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one warp waits, with a limit of `wait_ms`, for a ready flag that
+// nothing ever sets, and must come back with the timeout status instead of spinning forever.
+// Exercises exactly the wait the product kernels use, without disturbing any plan.
+// ------------------------------------------------------------------------------------------
+namespace {
+__global__ void wait_probe_kernel(i32* flag_and_status, u64 wait_ns) {
+    const bool ok = wait_ready(flag_and_status, 1, flag_and_status + 1, wait_ns);
+    if (threadIdx.x == 0) flag_and_status[2] = ok ? 1 : 0;
+}
+}  // namespace
+
+extern "C" int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* stream) {
+    if (wait_ms <= 0 || wait_ms > 1000)
+        return cbm::fail(CBM_B200_ERR_ARG, "selftest_wait: wait_ms must be in 1..1000");
+    DeviceGuard g(device);
+    if (!g.ok) return cbm::fail(CBM_B200_ERR_CUDA, "selftest_wait: cudaSetDevice failed");
+    i32* d = nullptr;
+    CBM_CUDA(cudaMalloc((void**)&d, 3 * sizeof(i32)));
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(d, 0, 3 * sizeof(i32), s);
+    i32 h[3] = {0, 0, -1};
+    if (e == cudaSuccess) {
+        wait_probe_kernel<<<1, 32, 0, s>>>(d, (u64)wait_ms * 1000000ULL);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(d);
+    if (e != cudaSuccess) return cbm::fail(CBM_B200_ERR_CUDA, std::string("selftest_wait: ") + cudaGetErrorString(e));
+    if (h[1] == CBM_B200_ERR_TIMEOUT && h[2] == 0)
+        return cbm::fail(CBM_B200_ERR_TIMEOUT, "selftest_wait: the wait ran out as it should");
+    return cbm::fail(CBM_B200_ERR_FORMAT, "selftest_wait: the wait did not report a timeout");
+}
+
+// ------------------------------------------------------------------------------------------
 // Product without any allocation in the call path.
 //
 // The ordinary product entry points grow the plan's ready-flag and partial-sum buffers with

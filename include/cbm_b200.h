@@ -165,6 +165,12 @@ int cbm_b200_csr_spmm(int32_t n_rows, const int32_t* row_b, const int32_t* row_e
 int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float* y, int32_t f,
                               int32_t normalized);
 
+/* Self-test of the device-side bounded wait (the reference has no counterpart: its CPU walk cannot
+ * stall).  One warp waits at most wait_ms (1..1000) for a flag that is never set; the call returns
+ * CBM_B200_ERR_TIMEOUT when the wait gave up as designed, any other status is a failure.  The
+ * context stays usable. */
+int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* stream);
+
 /* --------------------------------------------------------------------------------------------
  * The fused product for callers that must not allocate.  (No counterpart in the reference, whose
  * CPU kernels need no scratch memory; added for GPU callers.)

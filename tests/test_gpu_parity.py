@@ -339,3 +339,19 @@ def test_host_operands_pinned_and_pageable_agree(c1):
         got_pinned = torch.empty((n, f)).pin_memory()
         c.omp_mkl_csr_spmm_update(x.pin_memory(), got_pinned)
         assert torch.equal(got_pageable, want.cpu()) and torch.equal(got_pinned, want.cpu())
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(c1):
+    """A wait for a flag nothing sets must end by itself with the timeout status (50 ms limit);
+    afterwards the same context still computes correct products."""
+    L = _lib.lib()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert L.cbm_b200_selftest_wait(torch.cuda.current_device(), 50, st) == 4
+    assert b"ran out as it should" in L.cbm_b200_last_error()
+    assert L.cbm_b200_selftest_wait(torch.cuda.current_device(), 0, st) == 1
+    ei, c = c1
+    x = torch.randint(-3, 4, (c.num_rows, 8), device="cuda").float()
+    y = torch.empty_like(x)
+    c.omp_mkl_csr_spmm_update(x, y)
+    np.testing.assert_array_equal(y.cpu().numpy(), sparse_product(ei, x.cpu().numpy(), False).astype(np.float32))
+    c.plan().status()

@@ -721,6 +721,12 @@ Shape pick_shape(i32 f, i32 want_slab, bool can_v4) {
     s.v4 = can_v4;
     const i32 lane_w = s.v4 ? 128 : 32;  // columns covered by one vector per lane
     i32 slab = want_slab > 0 ? want_slab : (s.v4 ? 256 : 64);
+    if (s.v4 && (want_slab == 64 || want_slab == 32)) {  // narrow slabs on request: half-warp gather
+        s.nv = 1;
+        s.slab_w = want_slab;
+        s.n_slabs = (f + want_slab - 1) / want_slab;
+        return s;
+    }
     slab = std::max(lane_w, (slab / lane_w) * lane_w);
     slab = std::min(slab, lane_w * 4);
     const i32 f_up = ((f + lane_w - 1) / lane_w) * lane_w;

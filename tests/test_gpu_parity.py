@@ -355,3 +355,24 @@ def test_bounded_wait_reports_timeout_and_context_survives(c1):
     c.omp_mkl_csr_spmm_update(x, y)
     np.testing.assert_array_equal(y.cpu().numpy(), sparse_product(ei, x.cpu().numpy(), False).astype(np.float32))
     c.plan().status()
+
+
+def test_structure_in_reference_layout_is_consumed_unmodified(golden):
+    """A structure that already exists as (mst_row, mst_col, delta CSR, multiplier) arrays — what
+    the reference's own builder returns — runs without going through this package's builder.
+    Here the arrays come from the independent restatement, whose tree differs from the product
+    builder's wherever optimal trees tie."""
+    ei, x, y, y_norm = golden_case(golden, 3)
+    s = orc.build_structure(ei, 1)
+    c = cbm_matrix.from_arrays(s["mst_row"], s["mst_col"], s["crow"], s["col"], s["val"])
+    out = torch.empty((s["n"], x.shape[1]), device="cuda")
+    c.omp_mkl_csr_spmm_update(_dev(x), out)
+    np.testing.assert_array_equal(out.cpu().numpy(), y)
+    eil = with_self_loops(ei)
+    mult = orc.row_multiplier(eil, s["n"])
+    sn = orc.build_structure(eil, 2, col_mul=mult)
+    cn = cbm_matrix.from_arrays(sn["mst_row"], sn["mst_col"], sn["crow"], sn["col"], sn["val"], col_multiplier=mult)
+    outn = torch.empty_like(out)
+    cn.omp_mkl_csr_fused_spmm_update(_dev(x), outn)
+    np.testing.assert_allclose(outn.cpu().numpy(), y_norm, **TOL)
+    cn.check_format(torch.from_numpy(eil))

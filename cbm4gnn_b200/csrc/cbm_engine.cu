@@ -167,6 +167,20 @@ struct Vec<true> {
         return v;
     }
     static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg((const float4*)p); }
+    // L2-only fetch (data written earlier in the same launch), zeros when `on` is false; volatile
+    // asm for the same reason as ld_ro_if.
+    static __device__ __forceinline__ T ld_l2_if(const float* p, bool on) {
+        T v;
+        asm volatile(
+            "{\n\t.reg .pred q;\n\tsetp.ne.s32 q, %5, 0;\n\t"
+            "mov.f32 %0, 0f00000000;\n\tmov.f32 %1, 0f00000000;\n\t"
+            "mov.f32 %2, 0f00000000;\n\tmov.f32 %3, 0f00000000;\n\t"
+            "@q ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];\n\t}"
+            : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+            : "l"(p), "r"((int)on)
+            : "memory");
+        return v;
+    }
     static __device__ __forceinline__ void st(float* p, T v) { *(float4*)p = v; }
     static __device__ __forceinline__ T fma(float w, T a, T c) {
         c.x = fmaf(w, a.x, c.x);
@@ -199,6 +213,16 @@ struct Vec<false> {
         return v;
     }
     static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg(p); }
+    static __device__ __forceinline__ T ld_l2_if(const float* p, bool on) {
+        T v;
+        asm volatile(
+            "{\n\t.reg .pred q;\n\tsetp.ne.s32 q, %2, 0;\n\tmov.f32 %0, 0f00000000;\n\t"
+            "@q ld.global.cg.f32 %0, [%1];\n\t}"
+            : "=f"(v)
+            : "l"(p), "r"((int)on)
+            : "memory");
+        return v;
+    }
     static __device__ __forceinline__ void st(float* p, T v) { *p = v; }
     static __device__ __forceinline__ T fma(float w, T a, T c) { return fmaf(w, a, c); }
     static __device__ __forceinline__ T mul(float w, T a) { return w * a; }
@@ -357,13 +381,27 @@ __device__ __forceinline__ bool finish_item(const KParams& p, i32 slab, i32 pos,
     }
     const i32 n_part = (i32)((unsigned)info >> ITEM_NPART_SHIFT);
     if (n_part > 0 && p.mode != MODE_UPDATE_ONLY) {
-        for (i32 k = 0; k < n_part; ++k) {
-            if (!wait_ready(slab_flags + first_part + k, p.epoch, p.status, p.wait_ns)) return false;
-            const float* slot =
-                p.scratch + ((i64)slab * p.n_partial + first_part + k) * p.slab_w + lane * V::E;
+        // A row can have hundreds of parked shares; taking them one memory round trip at a time
+        // would serialise the whole product behind the longest row.  The 32 lanes wait for 32
+        // flags at once, then the shares are fetched PART_BATCH at a time and added in slot order
+        // (a fixed order, so results do not depend on timing).
+        bool mine = true;
+        for (i32 k = lane; k < n_part; k += 32)
+            mine = mine && wait_ready(slab_flags + first_part + k, p.epoch, p.status, p.wait_ns);
+        if (!__all_sync(0xffffffffu, mine)) return false;
+        constexpr int PART_BATCH = NV == 1 ? 8 : 4;
+        const float* slot0 = p.scratch + ((i64)slab * p.n_partial + first_part) * p.slab_w + lane * V::E;
+        for (i32 k = 0; k < n_part; k += PART_BATCH) {
+            typename V::T t[PART_BATCH][NV];
 #pragma unroll
-            for (int v = 0; v < NV; ++v)
-                if (ok[v]) acc[v] = V::fma(1.0f, V::ld_l2(slot + v * STEP), acc[v]);
+            for (int j = 0; j < PART_BATCH; ++j)
+#pragma unroll
+                for (int v = 0; v < NV; ++v)
+                    t[j][v] = V::ld_l2_if(slot0 + (i64)(k + j) * p.slab_w + v * STEP, ok[v] && (k + j) < n_part);
+#pragma unroll
+            for (int j = 0; j < PART_BATCH; ++j)
+#pragma unroll
+                for (int v = 0; v < NV; ++v) acc[v] = V::fma(1.0f, t[j][v], acc[v]);
         }
     }
     const i32 lane_col = c0 + lane * V::E;

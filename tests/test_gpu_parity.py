@@ -376,3 +376,23 @@ def test_structure_in_reference_layout_is_consumed_unmodified(golden):
     cn.omp_mkl_csr_fused_spmm_update(_dev(x), outn)
     np.testing.assert_allclose(outn.cpu().numpy(), y_norm, **TOL)
     cn.check_format(torch.from_numpy(eil))
+
+
+def test_giant_row_collects_hundreds_of_parked_shares():
+    """A hub row with 40 000 delta entries is cut into 313 segments; the finishing item must wait
+    for and add 312 parked shares (done 32 flags and 8 shares at a time)."""
+    n = 40001
+    hub = np.zeros(n - 1, dtype=np.int64)
+    leaf = np.arange(1, n, dtype=np.int64)
+    ei = np.stack([np.concatenate([hub, leaf]), np.concatenate([leaf, hub])])
+    # alpha above every row length: no compression is attempted (on a star the candidate search
+    # would visit all 40 000^2 leaf pairs, as the reference's A*A^T does), every row hangs off the
+    # virtual root and the hub row keeps all its entries
+    c = _cbm(ei, 100000)
+    assert int(np.diff(c._crow).max()) == n - 1
+    for f in (64, 500):
+        x = np.random.default_rng(f).integers(-2, 3, size=(n, f)).astype(np.float32)
+        out = torch.empty((n, f), device="cuda")
+        c.omp_mkl_csr_spmm_update(_dev(x), out)
+        np.testing.assert_array_equal(out.cpu().numpy(), sparse_product(ei, x, False).astype(np.float32))
+    c.plan().status()

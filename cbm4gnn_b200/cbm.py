@@ -197,6 +197,49 @@ class cbm_matrix:
                                               torch.from_numpy(self._dval), size=(n, n), check_invariants=False)
         return self
 
+    # ------------------------------------------------------------------ persistence
+    def state_dict(self) -> dict:
+        """Everything needed to rebuild this object without running the builder: the tree, the
+        delta CSR and the multiplier in the reference's layout, plus the build parameters."""
+        return dict(format="cbm4gnn_b200/1", num_rows=self.num_rows, alpha=self.alpha, normalized=self.normalized,
+                    nnz=self.nnz, mst_row=self.mst_row.clone(), mst_col=self.mst_col.clone(),
+                    delta_crow=torch.from_numpy(self._crow.copy()), delta_col=torch.from_numpy(self._dcol.copy()),
+                    delta_val=torch.from_numpy(self._dval.copy()),
+                    col_multiplier=None if self.col_multiplier is None else self.col_multiplier.clone(),
+                    edge_row=None if self._row is None else torch.from_numpy(self._row.copy()),
+                    edge_col=None if self._col is None else torch.from_numpy(self._col.copy()),
+                    build_info=dict(self.build_info))
+
+    def save(self, path) -> None:
+        """Write the built structure to ``path`` (the build is the expensive step: 20-60 s for
+        the high-degree configuration against under a millisecond per product)."""
+        torch.save(self.state_dict(), path)
+
+    @classmethod
+    def load(cls, path) -> "cbm_matrix":
+        """Rebuild an object written by ``save``; the arrays are used exactly as stored."""
+        st = torch.load(path, map_location="cpu", weights_only=False)
+        if st.get("format") != "cbm4gnn_b200/1":
+            raise ValueError(f"{path}: not a saved cbm_matrix")
+        self = cls.from_arrays(st["mst_row"], st["mst_col"], st["delta_crow"], st["delta_col"], st["delta_val"],
+                               col_multiplier=st["col_multiplier"])
+        self.alpha, self.nnz, self.build_info = st["alpha"], st["nnz"], st["build_info"]
+        if st["edge_row"] is not None:
+            self._row, self._col = _as_i32(st["edge_row"]), _as_i32(st["edge_col"])
+            self._symmetric = None
+        return self
+
+    def compression_ratio(self) -> float:
+        """Stored elements of the plain CSR (row pointers + columns + values) over stored elements
+        of this structure (delta row pointers + columns + values + mst_row + mst_col): the metric
+        of benchmark/utility.py:45-64."""
+        if self.nnz is None:
+            raise RuntimeError("the number of matrix entries is unknown for a structure wrapped from arrays")
+        n = self.num_rows
+        csr_total = (n + 1) + 2 * self.nnz
+        cbm_total = (n + 1) + 2 * int(self._crow[-1]) + self.mst_row.numel() + self.mst_col.numel()
+        return csr_total / cbm_total
+
     # ------------------------------------------------------------------ validation
     def check_format(self, edge_index):
         """Rebuild every row's column set from the tree and the signed deltas and compare it with

@@ -161,3 +161,20 @@ def test_builder_rejects_bad_input():
     assert L.cbm_b200_build(None, None, 2, 3, 0, None, 0, ctypes.byref(h)) == 1
     with pytest.raises(ValueError):
         cbm_matrix(torch.zeros((3, 4), dtype=torch.int32), torch.ones(4))
+
+
+def test_save_load_round_trip_and_compression_ratio(tmp_path):
+    ei = with_self_loops(graphs.make_graph("c1", scale=0.2))
+    c = _cbm(ei, 2, normalized=True)
+    path = tmp_path / "c.pt"
+    c.save(path)
+    d = cbm_matrix.load(path)
+    assert torch.equal(c.mst_row, d.mst_row) and torch.equal(c.mst_col, d.mst_col)
+    assert np.array_equal(c._crow, d._crow) and np.array_equal(c._dcol, d._dcol) and np.array_equal(c._dval, d._dval)
+    assert torch.equal(c.col_multiplier, d.col_multiplier) and d.alpha == 2 and d.normalized
+    assert d.is_symmetric() == c.is_symmetric()
+    d.check_format(torch.from_numpy(ei))
+    # the reference's metric: CSR elements over CBM elements (benchmark/utility.py:45-64)
+    n, nnz, nd = c.num_rows, ei.shape[1], c.build_info["n_delta"]
+    want = ((n + 1) + 2 * nnz) / ((n + 1) + 2 * nd + (n + 2) + n)
+    assert abs(c.compression_ratio() - want) < 1e-12 and abs(d.compression_ratio() - want) < 1e-12

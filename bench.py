@@ -70,8 +70,8 @@ def parse():
 def algorithmic_bytes(n_rows, n_delta, n_root_children, f, normalized=True):
     """Bytes one product must move: 4(N+1) row pointers + 4 nnzD indices + 4 F nnzD gathered rows
     + 4 F (N - roots) parent rows + 4 F N output + 8 N parent/scale words."""
-    return (4 * (n_rows + 1) + 4 * n_delta + 4 * f * n_delta + 4 * f * (n_rows - n_root_children)
-            + 4 * f * n_rows + 8 * n_rows)
+    from cbm4gnn_b200.alpha_search import product_bytes
+    return product_bytes(n_rows, n_delta, n_root_children, f)
 
 
 def make_workload(args, world):

@@ -178,3 +178,15 @@ def test_save_load_round_trip_and_compression_ratio(tmp_path):
     n, nnz, nd = c.num_rows, ei.shape[1], c.build_info["n_delta"]
     want = ((n + 1) + 2 * nnz) / ((n + 1) + 2 * nd + (n + 2) + n)
     assert abs(c.compression_ratio() - want) < 1e-12 and abs(d.compression_ratio() - want) < 1e-12
+
+
+def test_alpha_search_byte_model():
+    from cbm4gnn_b200.alpha_search import product_bytes, search_alpha
+    ei = torch.from_numpy(graphs.copy_model(1500, 0.95, 8, 5))
+    best, table = search_alpha(ei, f=64, alphas=(0, 2, 8, 1000), measure=False)
+    assert [r["alpha"] for r in table] == [0, 2, 8, 1000]
+    nd = [r["n_delta"] for r in table]
+    assert nd == sorted(nd) and table[-1]["n_root_children"] == int(ei.max()) + 1
+    assert best == min(table, key=lambda r: (r["bytes"], r["alpha"]))["alpha"] and best != 1000
+    r = table[0]
+    assert r["bytes"] == product_bytes(int(ei.max()) + 1, r["n_delta"], r["n_root_children"], 64)

@@ -396,3 +396,10 @@ def test_giant_row_collects_hundreds_of_parked_shares():
         c.omp_mkl_csr_spmm_update(_dev(x), out)
         np.testing.assert_array_equal(out.cpu().numpy(), sparse_product(ei, x, False).astype(np.float32))
     c.plan().status()
+
+
+def test_alpha_search_measures_on_the_gpu():
+    from cbm4gnn_b200.alpha_search import search_alpha
+    ei = torch.from_numpy(with_self_loops(graphs.copy_model(3000, 0.95, 8, 5)))
+    best, table = search_alpha(ei, f=64, alphas=(0, 4, 64), normalized=True, iters=5)
+    assert best in (0, 4, 64) and all(r["ms"] > 0 for r in table)

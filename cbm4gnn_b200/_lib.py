@@ -39,6 +39,7 @@ EXPORTED = [
     "cbm_b200_built_free",
     "cbm_b200_plan_create",
     "cbm_b200_plan_destroy",
+    "cbm_b200_schedule_info",
     "cbm_b200_plan_info",
     "cbm_b200_plan_tune",
     "cbm_b200_plan_status",
@@ -123,6 +124,8 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_plan_create", c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, POINTER(c_void_p))
     sig("cbm_b200_plan_destroy", None, c_void_p)
+    sig("cbm_b200_schedule_info", c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_int32, c_int32, c_int32, i32p, i32p, i32p, i32p)
     sig("cbm_b200_plan_info", c_int32, c_void_p, i32p, POINTER(c_int64), i32p, i32p,
         POINTER(c_int64))
     sig("cbm_b200_plan_tune", c_int32, c_void_p, c_int32, c_int32, c_int32, c_int32)

@@ -865,13 +865,68 @@ extern "C" void cbm_b200_plan_destroy(cbm_b200_plan* p) {
     delete p;
 }
 
-extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int32_t* mst_col,
-                                    const int32_t* delta_crow, const int32_t* delta_col,
-                                    const float* delta_val, const float* multiplier,
-                                    const int32_t* perm, int32_t n_labels, int32_t own_begin,
-                                    int32_t own_end, int32_t device, cbm_b200_plan** out) {
-    if (!out) return cbm::fail(CBM_B200_ERR_ARG, "plan_create: out is NULL");
-    *out = nullptr;
+namespace {
+
+// The host-side schedule of one plan, before anything touches the device.
+struct Schedule {
+    std::vector<RowDesc> desc;
+    std::vector<i32> pcol;
+    std::vector<float> pval;
+    i32 n_prefix = 0, n_partial = 0, n_rows_owned = 0, depth = 0, n_root_children = 0, n_labels = 0;
+};
+
+// Checks, before any launch, the properties the kernels rely on: items wait only for smaller
+// positions (so the in-order claiming cannot deadlock), whoever is waited for publishes, entry
+// ranges are consecutive, every output row is produced exactly once and every parked share is
+// collected exactly once.
+int validate_schedule(const Schedule& sch, i32 n_out) {
+    const i32 n_items = (i32)sch.desc.size();
+    auto bad = [](const char* what) { return cbm::fail(CBM_B200_ERR_FORMAT, std::string("schedule check: ") + what); };
+    if (sch.n_partial > sch.n_prefix || sch.n_prefix > n_items) return bad("prefix bounds");
+    std::vector<char> produced((size_t)std::max(n_out, 0), 0), collected((size_t)sch.n_partial, 0);
+    i64 cursor = 0;
+    for (i32 pos = 0; pos < n_items; ++pos) {
+        const RowDesc& d = sch.desc[pos];
+        const i32 len = (d.info >> ITEM_LEN_SHIFT) & 0xff;
+        const i32 n_part = (i32)((unsigned)d.info >> ITEM_NPART_SHIFT);
+        const bool partial = (d.info & ITEM_PARTIAL) != 0;
+        if (d.beg != cursor) return bad("entry ranges are not consecutive");
+        cursor += len;
+        if (partial != (pos < sch.n_partial)) return bad("PARTIAL items must fill positions [0, n_partial)");
+        if (partial) {
+            if (!(d.info & ITEM_PUBLISH) || d.parent_row >= 0 || n_part != 0) return bad("malformed PARTIAL item");
+            continue;
+        }
+        if (d.out_row < 0 || d.out_row >= n_out || produced[d.out_row]) return bad("output row missing or produced twice");
+        produced[d.out_row] = 1;
+        if (pos < sch.n_prefix && (d.parent_row >= 0 || n_part != 0)) return bad("a prefix item would have to wait");
+        if (d.parent_row >= 0) {
+            if (d.parent_pos < 0 || d.parent_pos >= pos) return bad("an item waits for a later position");
+            const RowDesc& q = sch.desc[d.parent_pos];
+            if ((q.info & ITEM_PARTIAL) || !(q.info & ITEM_PUBLISH) || q.out_row != d.parent_row)
+                return bad("parent item does not publish the row its child reads");
+        }
+        if (n_part > 0) {
+            if (pos < sch.n_prefix || d.first_part < 0 || d.first_part + n_part > sch.n_partial)
+                return bad("parked shares out of range");
+            for (i32 k = 0; k < n_part; ++k) {
+                if (collected[d.first_part + k]) return bad("a parked share is collected twice");
+                collected[d.first_part + k] = 1;
+            }
+        }
+    }
+    if (cursor != (i64)sch.pcol.size() || sch.pcol.size() != sch.pval.size()) return bad("entries not covered exactly once");
+    for (char c : collected)
+        if (!c) return bad("a parked share is never collected");
+    i32 rows = 0;
+    for (char c : produced) rows += c;
+    if (rows != sch.n_rows_owned) return bad("owned rows and produced rows differ");
+    return CBM_B200_OK;
+}
+
+int build_schedule(int32_t n, const int32_t* mst_row, const int32_t* mst_col, const int32_t* delta_crow,
+                   const int32_t* delta_col, const float* delta_val, const float* multiplier,
+                   const int32_t* perm, int32_t n_labels, int32_t own_begin, int32_t own_end, Schedule& sch) {
     if (n < 0 || !mst_row || !delta_crow || (n > 0 && !mst_col))
         return cbm::fail(CBM_B200_ERR_ARG, "plan_create: NULL tree or delta arrays");
     if (n_labels == 0) n_labels = n;
@@ -953,9 +1008,9 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
                                  "is not owned)");
             owned_rows.push_back(v);
         }
-    std::vector<RowDesc> desc;
-    std::vector<i32> pcol;
-    std::vector<float> pval;
+    std::vector<RowDesc>& desc = sch.desc;
+    std::vector<i32>& pcol = sch.pcol;
+    std::vector<float>& pval = sch.pval;
     pcol.reserve((size_t)nd_all);
     pval.reserve((size_t)nd_all);
     auto append_entries = [&](i32 v, i32 from, i32 to) {  // entries [from, to) of row v
@@ -1021,7 +1076,54 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
     // 3. everything that may wait, breadth-first: finishing items of split rows, rows with a parent
     for (i32 v : owned_rows)
         if (parent[v] != n || is_split(v)) add_row_item(v);
-    const i32 n_rows_owned = (i32)owned_rows.size();
+    sch.n_rows_owned = (i32)owned_rows.size();
+    sch.n_prefix = n_prefix;
+    sch.n_partial = n_partial;
+    sch.depth = depth;
+    sch.n_root_children = n_root_children;
+    sch.n_labels = n_labels;
+    return validate_schedule(sch, own_end - own_begin);
+}
+
+
+}  // namespace
+
+extern "C" int cbm_b200_schedule_info(int32_t n, const int32_t* mst_row, const int32_t* mst_col,
+                                      const int32_t* delta_crow, const int32_t* delta_col,
+                                      const float* delta_val, const float* multiplier,
+                                      const int32_t* perm, int32_t n_labels, int32_t own_begin,
+                                      int32_t own_end, int32_t* n_items, int32_t* n_prefix,
+                                      int32_t* n_partial, int32_t* n_rows) {
+    Schedule sch;
+    const int rc = build_schedule(n, mst_row, mst_col, delta_crow, delta_col, delta_val, multiplier, perm,
+                                  n_labels, own_begin, own_end, sch);
+    if (rc) return rc;
+    if (n_items) *n_items = (i32)sch.desc.size();
+    if (n_prefix) *n_prefix = sch.n_prefix;
+    if (n_partial) *n_partial = sch.n_partial;
+    if (n_rows) *n_rows = sch.n_rows_owned;
+    return CBM_B200_OK;
+}
+
+extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int32_t* mst_col,
+                                    const int32_t* delta_crow, const int32_t* delta_col,
+                                    const float* delta_val, const float* multiplier,
+                                    const int32_t* perm, int32_t n_labels, int32_t own_begin,
+                                    int32_t own_end, int32_t device, cbm_b200_plan** out) {
+    if (!out) return cbm::fail(CBM_B200_ERR_ARG, "plan_create: out is NULL");
+    *out = nullptr;
+    Schedule sch;
+    {
+        const int rc0 = build_schedule(n, mst_row, mst_col, delta_crow, delta_col, delta_val, multiplier, perm,
+                                       n_labels, own_begin, own_end, sch);
+        if (rc0) return rc0;
+    }
+    n_labels = sch.n_labels;
+    std::vector<RowDesc>& desc = sch.desc;
+    std::vector<i32>& pcol = sch.pcol;
+    std::vector<float>& pval = sch.pval;
+    const i32 n_rows_owned = sch.n_rows_owned, n_prefix = sch.n_prefix, n_partial = sch.n_partial;
+    const i32 depth = sch.depth, n_root_children = sch.n_root_children;
 
     int n_dev = 0;
     CBM_CUDA(cudaGetDeviceCount(&n_dev));

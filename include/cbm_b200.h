@@ -106,6 +106,16 @@ int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int32_t* mst_c
 
 void cbm_b200_plan_destroy(cbm_b200_plan* p);
 
+/* Host-only twin of cbm_b200_plan_create (same arguments minus the device): builds the schedule,
+ * runs the pre-launch checks (every item waits only for earlier items, whoever is waited for
+ * publishes, every row produced and every parked partial sum collected exactly once) and reports
+ * its sizes.  Needs no GPU; plan_create runs the same checks. */
+int cbm_b200_schedule_info(int32_t n, const int32_t* mst_row, const int32_t* mst_col,
+                           const int32_t* delta_crow, const int32_t* delta_col,
+                           const float* delta_val, const float* multiplier, const int32_t* perm,
+                           int32_t n_labels, int32_t own_begin, int32_t own_end, int32_t* n_items,
+                           int32_t* n_prefix, int32_t* n_partial, int32_t* n_rows);
+
 /* Figures used by the byte model: rows computed by this plan, delta entries of those rows, rows
  * whose parent is the virtual root, tree depth, and device bytes held by the plan. */
 int cbm_b200_plan_info(const cbm_b200_plan* p, int32_t* n_rows, int64_t* n_delta,

@@ -152,7 +152,6 @@ struct Vec<true> {
     using T = float4;
     static constexpr int E = 4;
     static __device__ __forceinline__ T zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
-    static __device__ __forceinline__ T ld_ro(const float* p) { return __ldg((const float4*)p); }
     // Read-only fetch that is skipped (giving zeros) when `on` is false.  Written as volatile asm
     // so that a batch of fetches stays a batch: the compiler may not sink one below its use.
     static __device__ __forceinline__ T ld_ro_if(const float* p, bool on) {
@@ -202,7 +201,6 @@ struct Vec<false> {
     using T = float;
     static constexpr int E = 1;
     static __device__ __forceinline__ T zero() { return 0.f; }
-    static __device__ __forceinline__ T ld_ro(const float* p) { return __ldg(p); }
     static __device__ __forceinline__ T ld_ro_if(const float* p, bool on) {
         T v;
         asm volatile(

@@ -39,6 +39,7 @@ sys.path.insert(0, ROOT)
 # captures summarised under profiles/ (key: workload, operand width, GPUs, scale).
 DRAM_TRAFFIC: dict = {
     ("c2", 500, 1, 1.0): 2.078e9,  # profiles/cbm_items_kernel_c2_f500.md
+    ("c4", 128, 1, 1.0): 1.238e9,  # profiles/cbm_items_kernel_c4_f128.md
 }
 
 

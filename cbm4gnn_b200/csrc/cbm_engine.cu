@@ -1248,8 +1248,10 @@ int plan_cfg(const cbm_b200_plan* p, const char* who, const float* x, i64 ldx, c
     } else {
         c.sh = pick_shape(f, p->slab_width, can_v4);
         // never-waiting items are claimed 4 at a time: measured best on B200 (fewer trips to the
-        // claim counter, which bounds short-row workloads; larger groups unbalance the long rows)
-        c.group = 4;
+        // claim counter, which bounds short-row workloads; larger groups unbalance the long rows).
+        // A small product keeps single claims: with fewer claims than resident warps, grouping
+        // only idles warps.
+        c.group = ((i64)p->n_prefix * c.sh.n_slabs >= (i64)p->sm_count * 256) ? 4 : 1;
     }
     c.n_pclaims = (p->n_prefix + c.group - 1) / c.group;
     c.claims_per_slab = c.n_pclaims + (p->n_items - p->n_prefix);

@@ -372,7 +372,8 @@ __device__ __forceinline__ bool finish_item(const KParams& p, i32 slab, i32 pos,
 #pragma unroll
         for (int v = 0; v < NV; ++v)
             if (ok[v]) V::st(slot + v * STEP, acc[v]);
-        __threadfence();
+        // the warp barrier orders every lane's stores before lane 0's release store, whose
+        // gpu-scope release then covers them all: no per-lane fence is needed
         __syncwarp();
         if (lane == 0) st_release(slab_flags + pos, p.epoch);
         return true;
@@ -422,7 +423,6 @@ __device__ __forceinline__ bool finish_item(const KParams& p, i32 slab, i32 pos,
     for (int v = 0; v < NV; ++v)
         if (ok[v]) V::st(yrow + v * STEP, acc[v]);
     if ((info & ITEM_PUBLISH) && p.mode != MODE_DELTA_ONLY) {
-        __threadfence();
         __syncwarp();
         if (lane == 0) st_release(slab_flags + pos, p.epoch);
     }

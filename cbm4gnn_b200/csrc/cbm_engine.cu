@@ -181,6 +181,7 @@ struct Vec<true> {
         return v;
     }
     static __device__ __forceinline__ void st(float* p, T v) { *(float4*)p = v; }
+    static __device__ __forceinline__ void st_stream(float* p, T v) { __stcs((float4*)p, v); }
     static __device__ __forceinline__ T fma(float w, T a, T c) {
         c.x = fmaf(w, a.x, c.x);
         c.y = fmaf(w, a.y, c.y);
@@ -222,6 +223,7 @@ struct Vec<false> {
         return v;
     }
     static __device__ __forceinline__ void st(float* p, T v) { *p = v; }
+    static __device__ __forceinline__ void st_stream(float* p, T v) { __stcs(p, v); }
     static __device__ __forceinline__ T fma(float w, T a, T c) { return fmaf(w, a, c); }
     static __device__ __forceinline__ T mul(float w, T a) { return w * a; }
 };
@@ -419,9 +421,17 @@ __device__ __forceinline__ bool finish_item(const KParams& p, i32 slab, i32 pos,
         }
     }
     float* yrow = p.y + (i64)out_row * p.ldy + lane_col;
+    if (info & ITEM_PUBLISH) {
 #pragma unroll
-    for (int v = 0; v < NV; ++v)
-        if (ok[v]) V::st(yrow + v * STEP, acc[v]);
+        for (int v = 0; v < NV; ++v)
+            if (ok[v]) V::st(yrow + v * STEP, acc[v]);
+    } else {
+        // nobody reads this row again during the product: a streaming store keeps it from
+        // pushing slabs of X out of L2
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+            if (ok[v]) V::st_stream(yrow + v * STEP, acc[v]);
+    }
     if ((info & ITEM_PUBLISH) && p.mode != MODE_DELTA_ONLY) {
         __syncwarp();
         if (lane == 0) st_release(slab_flags + pos, p.epoch);

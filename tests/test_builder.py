@@ -190,3 +190,23 @@ def test_alpha_search_byte_model():
     assert best == min(table, key=lambda r: (r["bytes"], r["alpha"]))["alpha"] and best != 1000
     r = table[0]
     assert r["bytes"] == product_bytes(int(ei.max()) + 1, r["n_delta"], r["n_root_children"], 64)
+
+
+def test_structure_is_pinned_byte_for_byte():
+    """Same seed, same structure: digests of (mst_row, mst_col, delta row pointers, columns, signs)
+    for two seeded graphs.  A change here means the builder's output changed (tie-breaking, order
+    of children, candidate rule) and every stored structure and measurement with it."""
+    import hashlib
+
+    def digest(c):
+        h = hashlib.sha256()
+        for a in (c.mst_row.numpy(), c.mst_col.numpy(), c._crow, c._dcol, np.sign(c._dval).astype(np.int8)):
+            h.update(np.ascontiguousarray(a).tobytes())
+        return h.hexdigest()
+
+    c = _cbm(graphs.make_graph("c1"), 0)
+    assert c.build_info["n_delta"] == 77490
+    assert digest(c) == "ef3d6b5c798651d5488d8e9447f7b25098500866faf946e00aaae1aca00752b4"
+    c = _cbm(with_self_loops(graphs.make_graph("c2", scale=0.1)), 8, normalized=True)
+    assert c.build_info["n_delta"] == 300192
+    assert digest(c) == "f096072e632b1da7ae1c82abf0c7dc8819e6cb691a62e957f0437f1c72097aba"

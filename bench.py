@@ -52,9 +52,10 @@ def parse():
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="with N > 1: weak = graph grows with N (default), strong = same graph sharded")
-    ap.add_argument("--task", default="spmm", choices=["spmm", "gcn"],
+    ap.add_argument("--task", default="spmm", choices=["spmm", "gcn", "build"],
                     help="spmm: one CBM product per step (the headline); gcn: forward+backward of the "
-                         "stacked GCN of the workload (1 GPU), reported in ms")
+                         "stacked GCN of the workload, reported in ms; build: host builder time and "
+                         "compression ratio over alpha in {0,1,2,4,...,64} (no GPU needed)")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (profiling captures)")
     ap.add_argument("--f", type=int, default=0, help="override the operand width")
     ap.add_argument("--alpha", type=int, default=-1, help="override the workload's alpha")
@@ -258,6 +259,39 @@ def gcn_task(args):
     return 0
 
 
+def build_task(args):
+    """Creation benchmark of the reference (benchmark/parallel/cbm_creation.py:13-14, 42-51): build the
+    structure for alpha in {0, 1, 2, 4, 8, 16, 32, 64}, report mean wall time of the constructor
+    over ``--steps`` builds (the reference uses 5) and the compression ratio.  Host only."""
+    import torch
+    from cbm4gnn_b200 import graphs
+    from cbm4gnn_b200.cbm import cbm_matrix
+    from cbm4gnn_b200.utility import add_self_loops
+    cfg = graphs.CONFIGS[args.workload]
+    e = torch.from_numpy(graphs.make_graph(args.workload, scale=args.scale))
+    if cfg["normalized"]:
+        e = add_self_loops(e)
+    e32, ones = e.to(torch.int32), torch.ones(e.shape[1])
+    iters = max(1, min(args.steps, 5))
+    rows = []
+    for alpha in (0, 1, 2, 4, 8, 16, 32, 64):
+        ts = []
+        for _ in range(iters):
+            t0 = time.perf_counter()
+            c = cbm_matrix(e32, ones, alpha=alpha, normalized=cfg["normalized"])
+            ts.append(time.perf_counter() - t0)
+        rows.append(dict(alpha=alpha, seconds_mean=float(np.mean(ts)), seconds_std=float(np.std(ts)),
+                         native_seconds=c.build_info["seconds_total"], n_delta=c.build_info["n_delta"],
+                         n_candidates=c.build_info["n_candidates"], depth=c.build_info["depth"],
+                         n_root_children=c.build_info["n_root_children"],
+                         compression_ratio=c.compression_ratio()))
+    print(json.dumps(dict(metric="cbm_creation_seconds", unit="s", higher_is_better=False, data="synthetic",
+                          config=dict(workload=args.workload, n=c.num_rows, nnz=int(e.shape[1]),
+                                      normalized=cfg["normalized"], host_threads=os.cpu_count(), builds_per_alpha=iters),
+                          value=rows[0]["seconds_mean"], per_alpha=rows)))
+    return 0
+
+
 def sharded_gcn_task(args, widths):
     """Forward pass of the workload's GCN stack with the structure sharded over the ranks
     (one NCCL all-gather per layer); strong scaling: the graph does not grow with N."""
@@ -324,6 +358,8 @@ def main():
     args = parse()
     if args.task == "gcn":
         return gcn_task(args)
+    if args.task == "build":
+        return build_task(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -52,10 +52,11 @@ def parse():
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="with N > 1: weak = graph grows with N (default), strong = same graph sharded")
-    ap.add_argument("--task", default="spmm", choices=["spmm", "gcn", "build"],
+    ap.add_argument("--task", default="spmm", choices=["spmm", "gcn", "build", "csr"],
                     help="spmm: one CBM product per step (the headline); gcn: forward+backward of the "
                          "stacked GCN of the workload, reported in ms; build: host builder time and "
-                         "compression ratio over alpha in {0,1,2,4,...,64} (no GPU needed)")
+                         "compression ratio over alpha in {0,1,2,4,...,64} (no GPU needed); csr: the "
+                         "uncompressed comparison — plain CSR product of the same (normalized) matrix")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (profiling captures)")
     ap.add_argument("--f", type=int, default=0, help="override the operand width")
     ap.add_argument("--alpha", type=int, default=-1, help="override the workload's alpha")
@@ -292,6 +293,65 @@ def build_task(args):
     return 0
 
 
+def csr_task(args):
+    """The comparison the reference makes (benchmark/parallel/benchmark_spmm_cpu.py:112-150): the same
+    matrix stored as plain CSR (weights deg^-1/2[row] deg^-1/2[col] when normalized) multiplied by the
+    library's CSR kernel, next to the CBM product of the same workload."""
+    import ctypes
+    import torch
+    from cbm4gnn_b200 import _lib
+    from cbm4gnn_b200.alpha_search import product_bytes
+    c, x, info = make_workload(args, 1)
+    L = _lib.lib()
+    dev = torch.device("cuda", 0)
+    n, f = c.num_rows, info["f"]
+    order = np.lexsort((c._col, c._row))
+    row, col = c._row[order], c._col[order]
+    crow = np.zeros(n + 1, dtype=np.int32)
+    np.cumsum(np.bincount(row, minlength=n), out=crow[1:])
+    if c.col_multiplier is not None:
+        s_ = c.col_multiplier.numpy()
+        val = (s_[row] * s_[col]).astype(np.float32)
+    else:
+        val = np.ones(row.shape[0], dtype=np.float32)
+    crow_d, col_d, val_d = (torch.from_numpy(a).to(dev) for a in (crow, col.astype(np.int32), val))
+    rb, re_ = crow_d[:-1].contiguous(), crow_d[1:].contiguous()
+    xd = torch.from_numpy(x).to(dev)
+    y_csr, y_cbm = torch.empty((n, f), device=dev), torch.empty((n, f), device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    plan = c.plan(0)
+    cbm_fn = L.cbm_b200_fused_spmm_update if c.normalized else L.cbm_b200_spmm_update
+
+    def run_csr():
+        _lib.check(L.cbm_b200_csr_spmm(n, rb.data_ptr(), re_.data_ptr(), col_d.data_ptr(), val_d.data_ptr(),
+                                       xd.data_ptr(), f, y_csr.data_ptr(), f, f, ctypes.c_void_p(st)))
+
+    def run_cbm():
+        _lib.check(cbm_fn(plan.handle, xd.data_ptr(), f, y_cbm.data_ptr(), f, f, ctypes.c_void_p(st)))
+
+    out = {}
+    for name, fn in (("csr", run_csr), ("cbm", run_cbm)):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = e0.elapsed_time(e1) / args.steps
+    err = float((y_csr - y_cbm).abs().max() / max(1e-30, float(y_csr.abs().max())))
+    nnz = int(row.shape[0])
+    print(json.dumps(dict(metric="csr_vs_cbm_spmm_ms", unit="ms", value=out["cbm"], higher_is_better=False,
+                          n_gpus=1, steps=args.steps, warmup=max(3, args.warmup), dtype="f32", data="synthetic",
+                          config=info, csr_ms=out["csr"], cbm_ms=out["cbm"], speedup_over_csr=out["csr"] / out["cbm"],
+                          csr_GBps=product_bytes(n, nnz, n, f) / out["csr"] / 1e6,
+                          cbm_GBps=product_bytes(n, info["n_delta"], info["n_root_children"], f) / out["cbm"] / 1e6,
+                          max_rel_difference=err)))
+    return 0 if err < 1e-4 else 1
+
+
 def sharded_gcn_task(args, widths):
     """Forward pass of the workload's GCN stack with the structure sharded over the ranks
     (one NCCL all-gather per layer); strong scaling: the graph does not grow with N."""
@@ -360,6 +420,8 @@ def main():
         return gcn_task(args)
     if args.task == "build":
         return build_task(args)
+    if args.task == "csr":
+        return csr_task(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -329,8 +329,13 @@ def csr_task(args):
     def run_cbm():
         _lib.check(cbm_fn(plan.handle, xd.data_ptr(), f, y_cbm.data_ptr(), f, f, ctypes.c_void_p(st)))
 
+    a_sp = torch.sparse_csr_tensor(crow_d.long(), col_d.long(), val_d, size=(n, n), check_invariants=False)
+
+    def run_lib():  # cuSPARSE through torch, for context
+        return a_sp @ xd
+
     out = {}
-    for name, fn in (("csr", run_csr), ("cbm", run_cbm)):
+    for name, fn in (("csr", run_csr), ("cbm", run_cbm), ("cusparse", run_lib)):
         for _ in range(max(3, args.warmup)):
             fn()
         torch.cuda.synchronize()
@@ -345,7 +350,8 @@ def csr_task(args):
     nnz = int(row.shape[0])
     print(json.dumps(dict(metric="csr_vs_cbm_spmm_ms", unit="ms", value=out["cbm"], higher_is_better=False,
                           n_gpus=1, steps=args.steps, warmup=max(3, args.warmup), dtype="f32", data="synthetic",
-                          config=info, csr_ms=out["csr"], cbm_ms=out["cbm"], speedup_over_csr=out["csr"] / out["cbm"],
+                          config=info, csr_ms=out["csr"], cbm_ms=out["cbm"], cusparse_csr_ms=out["cusparse"],
+                          speedup_over_csr=out["csr"] / out["cbm"], speedup_over_cusparse=out["cusparse"] / out["cbm"],
                           csr_GBps=product_bytes(n, nnz, n, f) / out["csr"] / 1e6,
                           cbm_GBps=product_bytes(n, info["n_delta"], info["n_root_children"], f) / out["cbm"] / 1e6,
                           max_rel_difference=err)))

@@ -115,7 +115,7 @@ class ClockSampler:
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self, index):
         self.index, self.proc, self.path = index, None, None
@@ -125,7 +125,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"],
+                                          "-i", str(self.index), "-lms", "20"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -139,7 +139,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, reasons, mx = [], set(), None
+        sm, util, reasons, mx = [], [], set(), None
         try:
             for line in open(self.path):
                 p = [t.strip() for t in line.split(",")]
@@ -148,6 +148,7 @@ class ClockSampler:
                 try:
                     sm.append(float(p[1]))
                     mx = float(p[2])
+                    util.append(float(p[9]) if len(p) > 9 else 0.0)
                 except ValueError:
                     continue
                 for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
@@ -157,8 +158,9 @@ class ClockSampler:
         except Exception:
             pass
         if sm:
-            busy = [v for v in sm if mx is None or v > 0.5 * mx] or sm
-            out = dict(sm_mhz=float(np.median(busy)), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+            busy = [v for v, u in zip(sm, util) if u > 0] or sm
+            out = dict(sm_mhz=float(np.median(busy)), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm),
+                       samples_under_load=len([u for u in util if u > 0]))
         return out
 
 
@@ -492,14 +494,16 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    plan.status(stream.cuda_stream)
-    barrier()
+    # nvidia-smi samples every 20 ms from before the warm-up to the end of the timed region; with
+    # the default K the timed region lasts a few tens of milliseconds, so only a few samples fall
+    # under load (those with GPU utilisation reported > 0 are the ones summarised)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+        time.sleep(0.05)
+    for _ in range(max(3, args.warmup)):
+        step()
+    plan.status(stream.cuda_stream)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
     ev[0].record()

@@ -134,7 +134,8 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
 
 #pragma omp parallel
     {
-        std::vector<i32> in_u((size_t)n, -1);  // column -> u if the column is in row u
+        std::vector<uint64_t> in_u(((size_t)n + 63) / 64, 0);  // bit per column: is it in row u?
+                                                                // (16 KB at n = 132 534: stays in L1)
         std::vector<i32> hits((size_t)n, 0);   // row -> shared columns seen inside u's prefix
         std::vector<i32> touched, cols;
 #pragma omp for schedule(dynamic, 1)
@@ -182,11 +183,11 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
                         const i32* ve = a.idx.data() + a.ptr[v + 1];
                         if ((i64)nv <= (i64)12 * (nu - plen)) {
                             if (!marked) {
-                                for (const i32* k = ub; k != ue; ++k) in_u[*k] = u;
+                                for (const i32* k = ub; k != ue; ++k) in_u[(size_t)*k >> 6] |= 1ull << (*k & 63);
                                 marked = true;
                             }
                             both = 0;
-                            for (const i32* k = vb; k != ve; ++k) both += (in_u[*k] == u);
+                            for (const i32* k = vb; k != ve; ++k) both += (i32)((in_u[(size_t)*k >> 6] >> (*k & 63)) & 1ull);
                         } else {
                             for (i32 i = plen; i < nu; ++i) both += std::binary_search(vb, ve, cols[i]);
                         }
@@ -194,6 +195,8 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
                     const i32 h = nu + nv - 2 * both;
                     if (h < nv - alpha) out.push_back({u, v, h});  // cbm/cbm_extensions.cpp:93-101
                 }
+                if (marked)
+                    for (const i32* k = ub; k != ue; ++k) in_u[(size_t)*k >> 6] = 0;
                 // only the few survivors are put in order (by child id); sorting every touched
                 // row first was the most expensive step of the whole search
                 std::sort(out.begin() + out_before, out.end(),

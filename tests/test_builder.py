@@ -210,3 +210,30 @@ def test_structure_is_pinned_byte_for_byte():
     c = _cbm(with_self_loops(graphs.make_graph("c2", scale=0.1)), 8, normalized=True)
     assert c.build_info["n_delta"] == 300192
     assert digest(c) == "f096072e632b1da7ae1c82abf0c7dc8819e6cb691a62e957f0437f1c72097aba"
+
+
+def test_random_small_patterns_are_valid_and_optimal():
+    """Property check of the arborescence solver and the candidate search on arbitrary (also
+    non-symmetric, also rank-deficient) small patterns: the structure must reproduce the matrix and
+    its weight must equal the optimum found by the independent O(V*E) solver of the restatement.
+    Small dense patterns produce many ties and nested cycles, the hard cases of the contraction."""
+    hyp = pytest.importorskip("hypothesis")
+    st = pytest.importorskip("hypothesis.strategies")
+
+    @hyp.settings(max_examples=60, deadline=None, derandomize=True)
+    @hyp.given(st.integers(2, 11), st.integers(0, 2 ** 31 - 1), st.floats(0.15, 0.9), st.integers(0, 3))
+    def check(n, seed, p, alpha):
+        rng = np.random.default_rng(seed)
+        mask = rng.random((n, n)) < p
+        mask[n - 1, rng.integers(0, n)] = True          # the matrix is n x n: last row is not empty
+        ei = np.stack(np.nonzero(mask)).astype(np.int64)
+        if int(ei.max()) + 1 != n:
+            mask[rng.integers(0, n), n - 1] = True
+            ei = np.stack(np.nonzero(mask)).astype(np.int64)
+        c = _cbm(ei, alpha)
+        c.check_format(torch.from_numpy(ei))
+        ref = orc.build_structure(ei, alpha)
+        assert c.build_info["n_delta"] == ref["weight"]
+        assert c.build_info["n_candidates"] == len(orc.candidate_edges(ei, n, alpha))
+
+    check()

@@ -720,7 +720,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) cbm_items_tma_kernel(const KPar
 
 // Plain CSR product (no tree): rows in natural order, one warp per (row, slab), grid-stride.
 template <int NV, bool V4>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (NV >= 4 ? 2 : 3))
     csr_rows_kernel(i32 n_rows, const i32* __restrict__ row_b, const i32* __restrict__ row_e,
                     const i32* __restrict__ col, const float* __restrict__ val,
                     const float* __restrict__ x, i64 ldx, float* __restrict__ y, i64 ldy, i32 f,
@@ -744,7 +744,7 @@ __global__ void __launch_bounds__(256)
             ok[v] = (lane * V::E + v * STEP) < wcols;
             acc[v] = V::zero();
         }
-        gather_row<NV, V4, (NV >= 4 ? 4 : 8)>(col, val, __ldg(row_b + row), __ldg(row_e + row), x + lane_col, ldx, ok,
+        gather_row<NV, V4, (NV == 1 ? 8 : 4)>(col, val, __ldg(row_b + row), __ldg(row_e + row), x + lane_col, ldx, ok,
                            acc, lane);
         float* yrow = y + (i64)row * ldy + lane_col;
 #pragma unroll

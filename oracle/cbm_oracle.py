@@ -4,12 +4,16 @@ Only ``tests/``, the smoke check and ``bench.py``'s CPU-baseline legs import thi
 product package never does.  The compute loops live in ``cbm_oracle.c`` (loaded with ctypes); this
 file restates the builder in numpy/scipy/pure Python for small inputs and wraps the C functions.
 
-Parity status: the reference ships no golden vectors and cannot be compiled offline (oneMKL and the
-arbok submodule are missing), so the restatement is pinned as the reference pins itself — against
-``A @ X`` from torch/dense at atol = rtol = 1e-4 (tests/test_matmul_correctness.py:43) — and by the
-fixtures under ``tests/golden/``.  The tree SHAPE depends on arbok's tie-breaking (unpinned
-upstream): "parity unpinned" for the shape; validity (``check_format``) and the optimal total
-weight are what is pinned.
+Parity status: pinned.  The reference ships no golden vectors of its own, so the pins are outputs
+of the reference itself: its unmodified native source compiled into ``oracle/_ref`` (stand-in
+headers for oneMKL and arbok, the sparse product forwarded to the oneMKL inside libtorch; see
+``build_ref.py``) and its unmodified Python class on top.  ``tests/golden/cbm_reference.npz`` holds
+such outputs for every product method; the tree updates of this file reproduce them bit for bit,
+the products within the reference's own atol = rtol = 1e-4 (tests/test_matmul_correctness.py:43),
+and where ``oracle/_ref`` is present the comparison is repeated live at benchmark sizes.
+The tree SHAPE depends on the arborescence solver's tie-breaking (arbok upstream, unpinned there):
+"parity unpinned" for the shape only; validity (``check_format``), the optimal total weight (equal
+to the reference builder's) and the delta values of shared (row, parent) pairs are pinned.
 """
 from __future__ import annotations
 

@@ -5,13 +5,14 @@
  * times beside it.  It is never linked into, imported by or called from the product
  * (cbm4gnn_b200/); only tests/, the smoke check and bench.py's cpu_baseline / reference legs load it.
  *
- * Parity status: the reference holds no golden vectors for this path (its tests are differential
- * against torch.sparse on random inputs, tests/test_matmul_correctness.py:30-61), and the
- * reference itself cannot be compiled here (needs Intel oneMKL headers and the un-vendored arbok
- * submodule).  The restatement is therefore pinned the way the reference pins itself: against
- * dense/torch-sparse A @ X at atol = rtol = 1e-4, plus committed fixtures generated from that
- * check.  For the tree SHAPE (an output of the external arbok solver, version unpinned) parity is
- * unpinned; only validity and optimal total weight are pinned.
+ * Parity status: pinned.  The reference holds no golden vectors for this path (its tests are
+ * differential against torch.sparse on random inputs, tests/test_matmul_correctness.py:30-61), so
+ * the pins are outputs of the reference itself: its unmodified cbm/cbm_extensions.cpp compiled into
+ * oracle/_ref (build_ref.py: stand-in headers for oneMKL and arbok, the sparse product forwarded to
+ * the oneMKL inside libtorch).  The update loops below reproduce the reference's bit for bit
+ * (committed fixtures tests/golden/cbm_reference.npz and live against oracle/_ref); the products
+ * agree within the reference's own atol = rtol = 1e-4.  For the tree SHAPE (an output of the
+ * arborescence solver's tie-breaking) parity is unpinned; validity and total weight are pinned.
  *
  * Each function names the reference lines (cbm/cbm_extensions.cpp) it follows.
  */

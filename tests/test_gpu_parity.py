@@ -399,7 +399,23 @@ def test_giant_row_collects_hundreds_of_parked_shares():
 
 
 def test_alpha_search_measures_on_the_gpu():
-    from cbm4gnn_b200.alpha_search import search_alpha
-    ei = torch.from_numpy(with_self_loops(graphs.copy_model(3000, 0.95, 8, 5)))
+    """Every alpha of the sweep is timed on the GPU; the structure the search settles on must
+    multiply correctly (against float64 CSR) and the table must agree with the builder's figures."""
+    from cbm4gnn_b200.alpha_search import product_bytes, search_alpha
+    ei_np = with_self_loops(graphs.copy_model(3000, 0.95, 8, 5))
+    ei = torch.from_numpy(ei_np)
     best, table = search_alpha(ei, f=64, alphas=(0, 4, 64), normalized=True, iters=5)
-    assert best in (0, 4, 64) and all(r["ms"] > 0 for r in table)
+    assert [r["alpha"] for r in table] == [0, 4, 64]
+    assert best == min(table, key=lambda r: (r["ms"], r["alpha"]))["alpha"]
+    assert all(0.001 < r["ms"] < 50 for r in table)
+    n = int(ei.max()) + 1
+    for r in table:
+        c = _cbm(ei_np, r["alpha"], normalized=True)
+        assert c.build_info["n_delta"] == r["n_delta"] and c.build_info["depth"] == r["depth"]
+        assert r["bytes"] == product_bytes(n, r["n_delta"], r["n_root_children"], 64)
+    assert table[0]["n_delta"] <= table[1]["n_delta"] <= table[2]["n_delta"]
+    x = np.random.default_rng(3).standard_normal((n, 64)).astype(np.float32)
+    c = _cbm(ei_np, best, normalized=True)
+    y = torch.empty((n, 64), device="cuda")
+    c.omp_mkl_csr_fused_spmm_update(_dev(x), y)
+    np.testing.assert_allclose(y.cpu().numpy(), sparse_product(ei_np, x, True), **TOL)

@@ -6,8 +6,8 @@ allocation's device synchronisation would break).  It runs the same kernel as th
 points but keeps its ready flags and partial sums in a fixed array inside the library, which is
 shared between calls and keeps the previous call's contents.  The test therefore makes two calls in
 a row, with different operands and a plan that has long rows (so partial sums are in play), and
-requires each to reproduce the ordinary entry point exactly: both run the same arithmetic in the
-same order.  The file name sorts last so that a run that stops at the first failure has already
+requires each to reproduce the ordinary entry point exactly (both run the same arithmetic in the
+same order) and to agree with an independent float64 CSR product of the same matrix.  The file name sorts last so that a run that stops at the first failure has already
 exercised everything else.
 """
 import ctypes
@@ -36,6 +36,11 @@ def test_static_scratch_product_matches_twice_in_a_row():
     plan = c.plan(torch.cuda.current_device())
     n = c.num_rows
     gen = torch.Generator(device="cuda").manual_seed(7)
+    import scipy.sparse as sp
+    e = ei.numpy()
+    a64 = sp.csr_matrix((np.ones(e.shape[1]), (e[0], e[1])), shape=(n, n))
+    s = np.asarray(a64.sum(1)).ravel() ** -0.5
+    a64_norm = sp.diags(s) @ a64 @ sp.diags(s)
     for normalized, f in ((1, 500), (0, 64)):
         x = torch.randn((n, f), device="cuda", generator=gen)
         want = torch.empty((n, f), device="cuda")
@@ -45,6 +50,9 @@ def test_static_scratch_product_matches_twice_in_a_row():
         plan.status()
         torch.testing.assert_close(got, want, atol=1e-4, rtol=1e-4)
         assert torch.equal(got, want)
+        # and both against an independent float64 CSR product of the same matrix
+        ref = a64 if not normalized else a64_norm
+        np.testing.assert_allclose(got.cpu().numpy(), ref @ x.cpu().numpy().astype(np.float64), atol=1e-4, rtol=1e-4)
 
 
 def test_static_scratch_rejects_oversized_products():

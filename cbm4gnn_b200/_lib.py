@@ -49,6 +49,9 @@ EXPORTED = [
     "cbm_b200_fused_update",
     "cbm_b200_delta_spmm",
     "cbm_b200_csr_spmm",
+    "cbm_b200_csr_plan_create",
+    "cbm_b200_spmm_update_bcast",
+    "cbm_b200_probe_l2_read_gbps",
     "cbm_b200_spmm_update_host",
     "cbm_b200_spmm_update_static",
     "cbm_b200_selftest_wait",
@@ -136,6 +139,11 @@ def lib() -> ctypes.CDLL:
         sig(name, c_int32, c_void_p, c_void_p, c_int64, c_int32, c_void_p)
     sig("cbm_b200_csr_spmm", c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
         c_int64, c_void_p, c_int64, c_int32, c_void_p)
+    sig("cbm_b200_csr_plan_create", c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32,
+        POINTER(c_void_p))
+    sig("cbm_b200_spmm_update_bcast", c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32,
+        c_int32, c_int32, POINTER(c_void_p), c_void_p)
+    sig("cbm_b200_probe_l2_read_gbps", c_double, c_int32)
     sig("cbm_b200_spmm_update_host", c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32)
     sig("cbm_b200_spmm_update_static", c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32,
         c_int32, c_void_p)

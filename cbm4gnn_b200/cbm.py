@@ -14,7 +14,8 @@ Differences from the reference that are deliberate:
   cbm/cbm.py:121);
 * nothing is printed;
 * ``seq_*`` and ``omp_*`` methods run the same kernels — on a GPU there is no thread-count knob;
-* ``matmul`` / ``matmul_t`` are additions: differentiable products used by the CUDA layers.
+* ``matmul`` and ``transposed`` are additions: the differentiable product used by the CUDA layers
+  and the structure its gradient runs on.
 """
 from __future__ import annotations
 
@@ -218,7 +219,7 @@ class cbm_matrix:
     @classmethod
     def load(cls, path) -> "cbm_matrix":
         """Rebuild an object written by ``save``; the arrays are used exactly as stored."""
-        st = torch.load(path, map_location="cpu", weights_only=False)
+        st = torch.load(path, map_location="cpu", weights_only=True)  # tensors and plain values only
         if st.get("format") != "cbm4gnn_b200/1":
             raise ValueError(f"{path}: not a saved cbm_matrix")
         self = cls.from_arrays(st["mst_row"], st["mst_col"], st["delta_crow"], st["delta_col"], st["delta_val"],
@@ -406,11 +407,13 @@ class cbm_matrix:
             self._transposed = t
         return self._transposed
 
-    def matmul(self, x: torch.Tensor) -> torch.Tensor:
+    def matmul(self, x: torch.Tensor, two_step: bool = False) -> torch.Tensor:
         """``A @ x`` (or ``D^-1/2 A D^-1/2 @ x`` when normalized) as a new tensor, differentiable
         with respect to ``x``.  The reference has no gradient for its CBM products (its in-place
-        native update is invisible to autograd); the gradient here is the transposed product."""
-        return _CBMMatmul.apply(x, self)
+        native update is invisible to autograd); the gradient here is the transposed product.
+        ``two_step`` runs the forward as the delta product followed by the update-only kernel, the
+        path of the reference's ``*_torch_csr_*matmul`` methods (cbm/cbm.py:255-275)."""
+        return _CBMMatmul.apply(x, self, two_step)
 
 
 def _product(cbm: "cbm_matrix", x: torch.Tensor) -> torch.Tensor:
@@ -434,10 +437,52 @@ def _product(cbm: "cbm_matrix", x: torch.Tensor) -> torch.Tensor:
 
 class _CBMMatmul(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, cbm):
+    def forward(ctx, x, cbm, two_step=False):
         ctx.cbm = cbm
+        if two_step:
+            x = x.contiguous()
+            return cbm.seq_torch_csr_fused_matmul(x) if cbm.normalized else cbm.seq_torch_csr_matmul(x)
         return _product(cbm, x)
 
     @staticmethod
     def backward(ctx, gy):
-        return _product(ctx.cbm.transposed(), gy), None
+        return _product(ctx.cbm.transposed(), gy), None, None
+
+
+class csr_matrix_plan:
+    """A plain fp32 CSR matrix resident on one GPU, multiplied by the same kernel as the CBM
+    products with every row hanging off the virtual root: the uncompressed comparison of
+    benchmark/parallel/benchmark_spmm_cpu.py:112-150 (there MKL's CSR product,
+    cbm/cbm_extensions.cpp:1707-1755).  Rows of any length are balanced over the GPU."""
+
+    def __init__(self, crow, col, val, n_cols: int, device_index: int | None = None):
+        crow, col, val = _as_i32(crow), _as_i32(col), _as_f32(val)
+        self.n_rows, self.n_cols = crow.shape[0] - 1, int(n_cols)
+        if device_index is None:
+            device_index = torch.cuda.current_device()
+        self.device_index = device_index
+        self.handle = ctypes.c_void_p(0)
+        _lib.check(_lib.lib().cbm_b200_csr_plan_create(self.n_rows, self.n_cols, _ptr(crow), _ptr(col), _ptr(val),
+                                                       device_index, ctypes.byref(self.handle)))
+
+    def matmul(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        _check_f32("rhs", x)
+        if x.size(0) != self.n_cols:
+            raise RuntimeError(f"shape mismatch: matrix is {self.n_rows}x{self.n_cols}, x {tuple(x.shape)}")
+        y = out if out is not None else torch.empty((self.n_rows, x.size(1)), dtype=x.dtype, device=x.device)
+        xp, ldx = _dense_args(x)
+        yp, ldy = _dense_args(y)
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(_lib.lib().cbm_b200_spmm_update(self.handle, xp, ldx, yp, ldy, int(x.size(1)), ctypes.c_void_p(stream)))
+        return y
+
+    def status(self, stream=0):
+        _lib.check(_lib.lib().cbm_b200_plan_status(self.handle, ctypes.c_void_p(stream)))
+
+    def __del__(self):
+        try:
+            if self.handle:
+                _lib.lib().cbm_b200_plan_destroy(self.handle)
+                self.handle = ctypes.c_void_p(0)
+        except Exception:
+            pass

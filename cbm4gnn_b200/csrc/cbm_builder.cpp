@@ -18,6 +18,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <memory>
 #include <vector>
 
 #include <omp.h>
@@ -476,7 +477,8 @@ extern "C" int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nn
     if (n_threads > 0) omp_set_num_threads(n_threads);
     int status = CBM_B200_OK;
     try {
-        auto* b = new cbm_b200_built();
+        // owned until it is handed to the caller: an exception on the way frees it
+        std::unique_ptr<cbm_b200_built> b(new cbm_b200_built());
         b->n = n;
         const double t0 = now_s();
         Pattern a = make_csr(row, col, nnz, n);
@@ -490,7 +492,6 @@ extern "C" int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nn
             b->seconds[0] = t1 - t0;
             std::string err;
             if (!solve_arborescence(g, n, arb, err)) {
-                delete b;
                 if (n_threads > 0) omp_set_num_threads(prev_threads);
                 return cbm::fail(CBM_B200_ERR_FORMAT, err);
             }
@@ -526,7 +527,6 @@ extern "C" int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nn
                 }
             }
             if ((i32)order.size() != n + 1) {
-                delete b;
                 if (n_threads > 0) omp_set_num_threads(prev_threads);
                 return cbm::fail(CBM_B200_ERR_FORMAT, "build: tree does not span every row");
             }
@@ -565,7 +565,6 @@ extern "C" int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nn
         for (i32 v = 0; v < n; ++v) {
             total += dlen[v];
             if (total > INT32_MAX) {
-                delete b;
                 if (n_threads > 0) omp_set_num_threads(prev_threads);
                 return cbm::fail(CBM_B200_ERR_ARG, "build: more than 2^31-1 delta entries");
             }
@@ -606,7 +605,7 @@ extern "C" int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nn
         }
         b->seconds[2] = now_s() - t2;
         b->seconds[3] = now_s() - t0;
-        *out = b;
+        *out = b.release();
     } catch (const std::bad_alloc&) {
         status = cbm::fail(CBM_B200_ERR_ALLOC, "build: out of host memory");
     }

@@ -24,6 +24,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "cbm_b200.h"
@@ -105,6 +106,13 @@ struct KParams {
     i32 mode;
     i32 use_scale;
     u64 wait_ns;
+    // Broadcast epilogue (multi-GPU): every finished row is also written, after the optional
+    // ReLU, to n_bcast further buffers with the layout of y — the slices that this shard occupies
+    // in the gathered layer output of each GPU (peer memory mapped into this process, reached
+    // by ordinary stores over NVLink).  y itself keeps the row as the tree needs it.
+    float* bcast[CBM_B200_MAX_BCAST];
+    i32 n_bcast;
+    i32 bcast_relu;
 };
 
 __device__ __forceinline__ i32 ld_acquire(const i32* p) {
@@ -196,6 +204,13 @@ struct Vec<true> {
         a.w *= w;
         return a;
     }
+    static __device__ __forceinline__ T relu(T a) {
+        a.x = fmaxf(a.x, 0.f);
+        a.y = fmaxf(a.y, 0.f);
+        a.z = fmaxf(a.z, 0.f);
+        a.w = fmaxf(a.w, 0.f);
+        return a;
+    }
 };
 template <>
 struct Vec<false> {
@@ -226,6 +241,7 @@ struct Vec<false> {
     static __device__ __forceinline__ void st_stream(float* p, T v) { __stcs(p, v); }
     static __device__ __forceinline__ T fma(float w, T a, T c) { return fmaf(w, a, c); }
     static __device__ __forceinline__ T mul(float w, T a) { return w * a; }
+    static __device__ __forceinline__ T relu(T a) { return fmaxf(a, 0.f); }
 };
 
 // acc[v] += sum over entries [beg,end) of val * X[col, slab columns of this lane].
@@ -390,6 +406,8 @@ __device__ __forceinline__ bool finish_item(const KParams& p, i32 slab, i32 pos,
         for (i32 k = lane; k < n_part; k += 32)
             mine = mine && wait_ready(slab_flags + first_part + k, p.epoch, p.status, p.wait_ns);
         if (!__all_sync(0xffffffffu, mine)) return false;
+        // lane k acquired flag k; the warp barrier extends that ordering to the lanes that did not
+        __syncwarp();
         constexpr int PART_BATCH = NV == 1 ? 8 : 4;
         const float* slot0 = p.scratch + ((i64)slab * p.n_partial + first_part) * p.slab_w + lane * V::E;
         for (i32 k = 0; k < n_part; k += PART_BATCH) {
@@ -435,6 +453,19 @@ __device__ __forceinline__ bool finish_item(const KParams& p, i32 slab, i32 pos,
     if ((info & ITEM_PUBLISH) && p.mode != MODE_DELTA_ONLY) {
         __syncwarp();
         if (lane == 0) st_release(slab_flags + pos, p.epoch);
+    }
+    if (p.n_bcast > 0) {
+        if (p.bcast_relu) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) acc[v] = V::relu(acc[v]);
+        }
+        const i64 off = (i64)out_row * p.ldy + lane_col;
+        for (int k = 0; k < p.n_bcast; ++k) {
+            float* dst = p.bcast[k] + off;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if (ok[v]) V::st(dst + v * STEP, acc[v]);
+        }
     }
     return true;
 }
@@ -673,6 +704,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) cbm_items_tma_kernel(const KPar
             issued = 1;
             if (n_batches > 1) load_idx(1, c_nx, w_nx);
         }
+        i32 waited = 0;  // batches whose arrival has been consumed
         for (i32 q = 0; q < n_batches && alive; ++q) {
             while (issued < n_batches && issued - q < STAGES) {  // keep the other stages busy
                 issue(issued, c_nx, w_nx);
@@ -685,6 +717,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) cbm_items_tma_kernel(const KPar
                 break;
             }
             parity ^= 1u << s;
+            waited = q + 1;
             const i32 e0 = e_begin + q * NB;
             const i32 cnt = min(NB, e_end - e0);
             const unsigned char* st = rows + (size_t)s * L::STAGE_BYTES + lane * 16;
@@ -703,7 +736,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) cbm_items_tma_kernel(const KPar
                                         acc[v]);
             }
         }
-        if (!alive) {  // a wait ran out: the status word is set, drain
+        if (!alive) {
+            // A wait ran out: the status word is set.  Copies already issued into this warp's
+            // shared-memory stages must land before the block may retire and its shared memory
+            // be handed on, so every outstanding stage is waited for (bounded) and discarded.
+            for (i32 qq = waited; qq < issued; ++qq) {
+                const int s2 = qq % STAGES;
+                mbar_wait(bar0 + 8 * s2, (parity >> s2) & 1u, p.status);
+                parity ^= 1u << s2;
+            }
             leave(p, lane);
             return;
         }
@@ -762,11 +803,24 @@ struct Shape {
     i32 slab_w;
     i32 n_slabs;
 };
-Shape pick_shape(i32 f, i32 want_slab, bool can_v4) {
+// Default slab width of the 128-bit path.  One slab of the operand (n_labels rows of slab_w floats)
+// is what every row gathers from while a slab is processed; it should stay resident in L2.  B200's
+// 126 MB L2 is two partitions that each keep their own copy of lines the SMs of both dies read, so
+// about half of it is usable for such an operand: 256-column slabs up to kL2SlabBytes, then
+// 128-column slabs up to the same bound, and 256 again beyond it (nothing stays resident anyway
+// and wide slabs need fewer passes over the indices).
+constexpr i64 kL2SlabBytes = 56ll << 20;
+i32 default_slab_v4(i64 n_labels) {
+    if (n_labels * 256 * 4 <= kL2SlabBytes) return 256;
+    if (n_labels * 128 * 4 <= kL2SlabBytes) return 128;
+    return 256;
+}
+
+Shape pick_shape(i32 f, i32 want_slab, bool can_v4, i64 n_labels) {
     Shape s{};
     s.v4 = can_v4;
     const i32 lane_w = s.v4 ? 128 : 32;  // columns covered by one vector per lane
-    i32 slab = want_slab > 0 ? want_slab : (s.v4 ? 256 : 64);
+    i32 slab = want_slab > 0 ? want_slab : (s.v4 ? default_slab_v4(n_labels) : 64);
     if (s.v4 && (want_slab == 64 || want_slab == 32)) {  // narrow slabs on request: half-warp gather
         s.nv = 1;
         s.slab_w = want_slab;
@@ -932,9 +986,26 @@ int validate_schedule(const Schedule& sch, i32 n_out) {
     return CBM_B200_OK;
 }
 
+// csr_cols > 0 schedules a plain CSR matrix with that many columns (no tree: every row hangs off
+// the virtual root, mst_row / mst_col / perm are not read); csr_cols == 0 schedules a CBM structure.
 int build_schedule(int32_t n, const int32_t* mst_row, const int32_t* mst_col, const int32_t* delta_crow,
                    const int32_t* delta_col, const float* delta_val, const float* multiplier,
-                   const int32_t* perm, int32_t n_labels, int32_t own_begin, int32_t own_end, Schedule& sch) {
+                   const int32_t* perm, int32_t n_labels, int32_t own_begin, int32_t own_end, Schedule& sch,
+                   int32_t csr_cols = 0) {
+    std::vector<i32> flat_row, flat_col;
+    if (csr_cols > 0) {
+        if (n < 0 || !delta_crow) return cbm::fail(CBM_B200_ERR_ARG, "csr_plan_create: NULL row pointers");
+        flat_row.assign((size_t)n + 2, 0);
+        flat_row[(size_t)n + 1] = n;
+        flat_col.resize((size_t)n);
+        for (i32 v = 0; v < n; ++v) flat_col[v] = v;
+        mst_row = flat_row.data();
+        mst_col = flat_col.data();
+        perm = nullptr;
+        n_labels = n;  // labels of the rows; the column bound is csr_cols
+        own_begin = 0;
+        own_end = n;
+    }
     if (n < 0 || !mst_row || !delta_crow || (n > 0 && !mst_col))
         return cbm::fail(CBM_B200_ERR_ARG, "plan_create: NULL tree or delta arrays");
     if (n_labels == 0) n_labels = n;
@@ -945,6 +1016,7 @@ int build_schedule(int32_t n, const int32_t* mst_row, const int32_t* mst_col, co
     const i64 nd_all = delta_crow[n];
     if (nd_all > 0 && (!delta_col || !delta_val))
         return cbm::fail(CBM_B200_ERR_ARG, "plan_create: NULL delta col/val");
+    const i32 col_bound = csr_cols > 0 ? csr_cols : n;
 
     // ---- validate the tree: every row exactly once, reachable from the virtual root ----
     if (mst_row[0] != 0 || mst_row[n + 1] != n)
@@ -984,7 +1056,7 @@ int build_schedule(int32_t n, const int32_t* mst_row, const int32_t* mst_col, co
             return cbm::fail(CBM_B200_ERR_FORMAT, "plan_create: delta_crow not monotone");
     }
     for (i64 k = 0; k < nd_all; ++k)
-        if (delta_col[k] < 0 || delta_col[k] >= n)
+        if (delta_col[k] < 0 || delta_col[k] >= col_bound)
             return cbm::fail(CBM_B200_ERR_FORMAT, "plan_create: delta column out of range");
     if (perm) {
         std::vector<char> seen((size_t)n_labels, 0);
@@ -1089,7 +1161,7 @@ int build_schedule(int32_t n, const int32_t* mst_row, const int32_t* mst_col, co
     sch.n_partial = n_partial;
     sch.depth = depth;
     sch.n_root_children = n_root_children;
-    sch.n_labels = n_labels;
+    sch.n_labels = csr_cols > 0 ? csr_cols : n_labels;
     return validate_schedule(sch, own_end - own_begin);
 }
 
@@ -1113,6 +1185,11 @@ extern "C" int cbm_b200_schedule_info(int32_t n, const int32_t* mst_row, const i
     return CBM_B200_OK;
 }
 
+namespace {
+int plan_from_schedule(Schedule& sch, int32_t n, int32_t n_out, bool normalized, int32_t device,
+                       cbm_b200_plan** out);
+}
+
 extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int32_t* mst_col,
                                     const int32_t* delta_crow, const int32_t* delta_col,
                                     const float* delta_val, const float* multiplier,
@@ -1121,12 +1198,28 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
     if (!out) return cbm::fail(CBM_B200_ERR_ARG, "plan_create: out is NULL");
     *out = nullptr;
     Schedule sch;
-    {
-        const int rc0 = build_schedule(n, mst_row, mst_col, delta_crow, delta_col, delta_val, multiplier, perm,
-                                       n_labels, own_begin, own_end, sch);
-        if (rc0) return rc0;
-    }
-    n_labels = sch.n_labels;
+    const int rc0 = build_schedule(n, mst_row, mst_col, delta_crow, delta_col, delta_val, multiplier, perm,
+                                   n_labels, own_begin, own_end, sch);
+    if (rc0) return rc0;
+    return plan_from_schedule(sch, n, own_end - own_begin, multiplier != nullptr, device, out);
+}
+
+extern "C" int cbm_b200_csr_plan_create(int32_t n_rows, int32_t n_cols, const int32_t* crow,
+                                        const int32_t* col, const float* val, int32_t device,
+                                        cbm_b200_plan** out) {
+    if (!out) return cbm::fail(CBM_B200_ERR_ARG, "csr_plan_create: out is NULL");
+    *out = nullptr;
+    if (n_cols <= 0) return cbm::fail(CBM_B200_ERR_ARG, "csr_plan_create: n_cols must be positive");
+    Schedule sch;
+    const int rc0 = build_schedule(n_rows, nullptr, nullptr, crow, col, val, nullptr, nullptr, 0, 0, 0, sch, n_cols);
+    if (rc0) return rc0;
+    return plan_from_schedule(sch, n_rows, n_rows, false, device, out);
+}
+
+namespace {
+int plan_from_schedule(Schedule& sch, int32_t n, int32_t n_out, bool normalized, int32_t device,
+                       cbm_b200_plan** out) {
+    const int32_t n_labels = sch.n_labels;
     std::vector<RowDesc>& desc = sch.desc;
     std::vector<i32>& pcol = sch.pcol;
     std::vector<float>& pval = sch.pval;
@@ -1145,7 +1238,7 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
     p->device = device;
     p->n = n;
     p->n_labels = n_labels;
-    p->n_out = own_end - own_begin;
+    p->n_out = n_out;
     p->n_rows = n_rows_owned;
     p->n_items = (i32)desc.size();
     p->n_prefix = n_prefix;
@@ -1153,7 +1246,7 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
     p->n_delta = (i64)pcol.size();
     p->n_root_children = n_root_children;
     p->depth = depth;
-    p->normalized = multiplier != nullptr;
+    p->normalized = normalized;
     cudaDeviceProp prop{};
     if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) p->sm_count = prop.multiProcessorCount;
     int rc = upload(&p->d_desc, desc, p->device_bytes);
@@ -1178,6 +1271,7 @@ extern "C" int cbm_b200_plan_create(int32_t n, const int32_t* mst_row, const int
     *out = p;
     return CBM_B200_OK;
 }
+}  // namespace
 
 extern "C" int cbm_b200_plan_info(const cbm_b200_plan* p, int32_t* n_rows, int64_t* n_delta,
                                   int32_t* n_root_children, int32_t* depth,
@@ -1196,8 +1290,8 @@ extern "C" int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t 
     if (!p) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: NULL plan");
     if (slab_width < 0 || n_blocks < 0 || host_chunk < 0 || form < 0 || form > 1)
         return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: knob out of range");
-    p->form = form;
     if (host_chunk % 4 != 0) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: host_chunk must be a multiple of 4");
+    p->form = form;
     p->slab_width = slab_width;
     p->n_blocks = n_blocks;
     p->host_chunk = host_chunk;
@@ -1256,7 +1350,7 @@ int plan_cfg(const cbm_b200_plan* p, const char* who, const float* x, i64 ldx, c
         c.sh.n_slabs = (f + slab - 1) / slab;
         c.group = 16;
     } else {
-        c.sh = pick_shape(f, p->slab_width, can_v4);
+        c.sh = pick_shape(f, p->slab_width, can_v4, p->n_labels);
         // never-waiting items are claimed 4 at a time: measured best on B200 (fewer trips to the
         // claim counter, which bounds short-row workloads; larger groups unbalance the long rows).
         // A small product keeps single claims: with fewer claims than resident warps, grouping
@@ -1305,10 +1399,21 @@ int launch_regs(KParams& kp, int want_blocks, int sm_count, cudaStream_t s) {
 }
 
 // Fills the launch parameters that do not depend on where the scratch lives, and launches.
+struct Bcast {
+    int n = 0;
+    int relu = 0;
+    float* dst[CBM_B200_MAX_BCAST] = {nullptr};
+};
+
 int launch_plan(cbm_b200_plan* p, const LaunchCfg& c, const float* x, i64 ldx, float* y, i64 ldy, i32 f,
                 int mode, bool use_scale, u64* counter, i32* flags, float* scratch, i32 epoch,
-                cudaStream_t s) {
+                cudaStream_t s, const Bcast* bc = nullptr) {
     KParams kp{};
+    if (bc) {
+        kp.n_bcast = bc->n;
+        kp.bcast_relu = bc->relu;
+        for (int k = 0; k < bc->n; ++k) kp.bcast[k] = bc->dst[k];
+    }
     kp.desc = p->d_desc;
     kp.col = p->d_col;
     kp.val = p->d_val;
@@ -1345,7 +1450,7 @@ int launch_plan(cbm_b200_plan* p, const LaunchCfg& c, const float* x, i64 ldx, f
 }
 
 int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* y, i64 ldy, i32 f,
-             int mode, bool use_scale, cudaStream_t s) {
+             int mode, bool use_scale, cudaStream_t s, const Bcast* bc = nullptr) {
     if (!p) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": NULL plan");
     int rc = check_dense(who, x, ldx, y, ldy, f);
     if (rc) return rc;
@@ -1387,7 +1492,7 @@ int run_plan(cbm_b200_plan* p, const char* who, const float* x, i64 ldx, float* 
         p->epoch = 0;
     }
     return launch_plan(p, c, x, ldx, y, ldy, f, mode, use_scale, p->d_counter, p->d_flags, p->d_scratch,
-                       ++p->epoch, s);
+                       ++p->epoch, s, bc);
 }
 
 }  // namespace
@@ -1416,6 +1521,27 @@ extern "C" int cbm_b200_delta_spmm(cbm_b200_plan* p, const float* x, int64_t ldx
                     (cudaStream_t)stream);
 }
 
+extern "C" int cbm_b200_spmm_update_bcast(cbm_b200_plan* p, const float* x, int64_t ldx, float* y,
+                                          int64_t ldy, int32_t f, int32_t normalized, int32_t relu,
+                                          int32_t n_dst, float* const* dst, void* stream) {
+    if (n_dst < 0 || n_dst > CBM_B200_MAX_BCAST || (n_dst > 0 && !dst))
+        return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_bcast: between 0 and " +
+                                               std::to_string(CBM_B200_MAX_BCAST) + " destinations");
+    Bcast bc;
+    bc.n = n_dst;
+    bc.relu = relu != 0;
+    const bool v4 = (f % 4 == 0) && (ldy % 4 == 0);
+    for (int k = 0; k < n_dst; ++k) {
+        if (!dst[k]) return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_bcast: NULL destination");
+        if (dst[k] == x) return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_bcast: a destination aliases x");
+        if (v4 && aligned16(y) && !aligned16(dst[k]))
+            return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_bcast: destinations must be 16-byte aligned like y");
+        bc.dst[k] = dst[k];
+    }
+    return run_plan(p, "spmm_update_bcast", x, ldx, y, ldy, f, MODE_FUSED, normalized != 0,
+                    (cudaStream_t)stream, &bc);
+}
+
 extern "C" int cbm_b200_csr_spmm(int32_t n_rows, const int32_t* row_b, const int32_t* row_e,
                                  const int32_t* col, const float* val, const float* x,
                                  int64_t ldx, float* y, int64_t ldy, int32_t f, void* stream) {
@@ -1426,7 +1552,7 @@ extern "C" int cbm_b200_csr_spmm(int32_t n_rows, const int32_t* row_b, const int
     if (!x) return cbm::fail(CBM_B200_ERR_ARG, "csr_spmm: x is NULL");
     if (n_rows == 0) return CBM_B200_OK;
     const bool can_v4 = (f % 4 == 0) && (ldy % 4 == 0) && (ldx % 4 == 0) && aligned16(y) && aligned16(x);
-    const Shape sh = pick_shape(f, 0, can_v4);
+    const Shape sh = pick_shape(f, 256, can_v4, 0);
     const i64 n_units = (i64)sh.n_slabs * n_rows;
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess)
@@ -1455,8 +1581,11 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
     if (!p) return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_host: NULL plan");
     if (!x || !y || f <= 0) return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_host: bad x / y / f");
     DeviceGuard g(p->device);
-    // leading dimension rounded up to 4 floats so the 128-bit path applies to any f % 4 == 0
-    const i64 xb = (i64)p->n_labels * f, yb = (i64)p->n_out * f;
+    // The staging buffers use a leading dimension rounded up to 4 floats, so that rows stay
+    // 16-byte aligned whatever f is; chunks whose width is a multiple of 4 then take the 128-bit
+    // path; a ragged last chunk is cut into a 128-bit part and a scalar tail of 1-3 columns.
+    const i64 ld = ((i64)f + 3) / 4 * 4;
+    const i64 xb = (i64)p->n_labels * ld, yb = (i64)p->n_out * ld;
     if (xb > p->stage_x_cap) {
         cudaFree(p->stage_x);
         p->stage_x = nullptr;
@@ -1477,7 +1606,17 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
     // and chunk k-1 of y on its way out (PCIe is full duplex), so the call costs about one
     // transfer of x plus the last chunk's product and transfer instead of x + product + y.
     const i32 chunk = p->host_chunk > 0 ? p->host_chunk : 128;
-    const i32 n_chunks = (f + chunk - 1) / chunk;
+    std::vector<std::pair<i32, i32>> chunks;  // (first column, width)
+    for (i32 c0 = 0; c0 < f; c0 += chunk) {
+        const i32 w = std::min(chunk, f - c0);
+        if (w % 4 != 0 && w > 4) {  // ragged end: a 128-bit part and a short scalar tail
+            chunks.emplace_back(c0, w / 4 * 4);
+            chunks.emplace_back(c0 + w / 4 * 4, w % 4);
+        } else {
+            chunks.emplace_back(c0, w);
+        }
+    }
+    const i32 n_chunks = (i32)chunks.size();
     if (!p->copy_in) CBM_CUDA(cudaStreamCreateWithFlags(&p->copy_in, cudaStreamNonBlocking));
     if (!p->copy_out) CBM_CUDA(cudaStreamCreateWithFlags(&p->copy_out, cudaStreamNonBlocking));
     while ((i32)p->events.size() < 2 * n_chunks) {
@@ -1486,20 +1625,20 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
         p->events.push_back(e);
     }
     cudaStream_t s = p->own_stream;
-    const size_t pitch = (size_t)f * sizeof(float);
+    const size_t pitch = (size_t)f * sizeof(float), dpitch = (size_t)ld * sizeof(float);
     for (i32 k = 0; k < n_chunks; ++k) {
-        const i32 c0 = k * chunk;
-        const i32 w = std::min(chunk, f - c0);
-        CBM_CUDA(cudaMemcpy2DAsync(p->stage_x + c0, pitch, x + c0, pitch, (size_t)w * sizeof(float),
+        const i32 c0 = chunks[k].first;
+        const i32 w = chunks[k].second;
+        CBM_CUDA(cudaMemcpy2DAsync(p->stage_x + c0, dpitch, x + c0, pitch, (size_t)w * sizeof(float),
                                        (size_t)p->n_labels, cudaMemcpyHostToDevice, p->copy_in));
         CBM_CUDA(cudaEventRecord(p->events[2 * k], p->copy_in));
         CBM_CUDA(cudaStreamWaitEvent(s, p->events[2 * k], 0));
-        int rc = run_plan(p, "spmm_update_host", p->stage_x + c0, f, p->stage_y + c0, f, w, MODE_FUSED,
+        int rc = run_plan(p, "spmm_update_host", p->stage_x + c0, ld, p->stage_y + c0, ld, w, MODE_FUSED,
                           normalized != 0, s);
         if (rc) return rc;
         CBM_CUDA(cudaEventRecord(p->events[2 * k + 1], s));
         CBM_CUDA(cudaStreamWaitEvent(p->copy_out, p->events[2 * k + 1], 0));
-        CBM_CUDA(cudaMemcpy2DAsync(y + c0, pitch, p->stage_y + c0, pitch, (size_t)w * sizeof(float),
+        CBM_CUDA(cudaMemcpy2DAsync(y + c0, pitch, p->stage_y + c0, dpitch, (size_t)w * sizeof(float),
                                    (size_t)p->n_out, cudaMemcpyDeviceToHost, p->copy_out));
     }
     CBM_CUDA(cudaStreamSynchronize(p->copy_out));
@@ -1539,6 +1678,66 @@ extern "C" int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* str
     if (h[1] == CBM_B200_ERR_TIMEOUT && h[2] == 0)
         return cbm::fail(CBM_B200_ERR_TIMEOUT, "selftest_wait: the wait ran out as it should");
     return cbm::fail(CBM_B200_ERR_FORMAT, "selftest_wait: the wait did not report a timeout");
+}
+
+// ------------------------------------------------------------------------------------------
+// Measurement aid: the rate at which all SMs together stream a buffer that is resident in L2
+// (32 MB, read 64 times with L2-only 128-bit loads, eight independent loads in flight per thread).
+// The product kernels gather operand rows out of L2, so this rate — not the HBM rate — is the
+// ceiling of their gather traffic; bench.py reports the gather rate against it.
+// ------------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(512) l2_read_probe_kernel(const float4* __restrict__ buf, u64 n_vec, int rounds,
+                                                            float* sink) {
+    const u64 stride = (u64)gridDim.x * blockDim.x;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < rounds; ++r) {
+        for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i + 7 * stride < n_vec; i += 8 * stride) {
+            float4 t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = __ldcg(buf + i + (u64)k * stride);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                a.x += t[k].x;
+                a.y += t[k].y;
+                a.z += t[k].z;
+                a.w += t[k].w;
+            }
+        }
+    }
+    if (a.x + a.y + a.z + a.w == 12345.678f) *sink = a.x;  // keeps the loads alive
+}
+}  // namespace
+
+extern "C" double cbm_b200_probe_l2_read_gbps(int32_t device) {
+    DeviceGuard g(device);
+    if (!g.ok) return -1.0;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int threads = 512, blocks = sms * 4;
+    const u64 per_pass = (u64)blocks * threads * 8;            // vectors read per sweep of the grid
+    const u64 n_vec = ((32ull << 20) / 16) / per_pass * per_pass;  // about 32 MB, a whole number of sweeps
+    float4* buf = nullptr;
+    float* sink = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    double out = -1.0;
+    if (cudaMalloc((void**)&buf, n_vec * 16) == cudaSuccess && cudaMalloc((void**)&sink, 4) == cudaSuccess &&
+        cudaMemset(buf, 0, n_vec * 16) == cudaSuccess && cudaEventCreate(&e0) == cudaSuccess &&
+        cudaEventCreate(&e1) == cudaSuccess) {
+        const int rounds = 64;
+        l2_read_probe_kernel<<<blocks, threads>>>(buf, n_vec, 4, sink);  // warm-up: brings the buffer into L2
+        cudaEventRecord(e0);
+        l2_read_probe_kernel<<<blocks, threads>>>(buf, n_vec, rounds, sink);
+        cudaEventRecord(e1);
+        float ms = 0.f;
+        if (cudaEventSynchronize(e1) == cudaSuccess && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess && ms > 0.f)
+            out = (double)n_vec * 16.0 * rounds / (ms * 1e-3) / 1e9;
+    }
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(buf);
+    cudaFree(sink);
+    return out;
 }
 
 // ------------------------------------------------------------------------------------------

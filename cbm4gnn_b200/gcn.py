@@ -30,17 +30,33 @@ def _fp32_linear(lin: nn.Linear, x: torch.Tensor) -> torch.Tensor:
 
 
 class CBMCudaGCN(CBMCudaMessagePassing):
-    def __init__(self, in_channels: int, out_channels: int, alpha: int = 2):
+    """``order``: "lin_first" is the reference's ``propagate(lin(x))`` (cbm_gcn.py:21-24);
+    "propagate_first" computes ``lin(propagate(x))``, the same matrix product ``A (X W) = (A X) W``
+    with the sparse product running at the input width; "auto" (default) propagates at the
+    narrower of the two widths."""
+
+    def __init__(self, in_channels: int, out_channels: int, alpha: int = 2, order: str = "auto"):
         super().__init__(normalize=True, alpha=alpha)
+        if order not in ("auto", "lin_first", "propagate_first"):
+            raise ValueError("order must be 'auto', 'lin_first' or 'propagate_first'")
         self.in_channels = in_channels
         self.out_channels = out_channels
+        self.order = order
         self.lin = nn.Linear(in_channels, out_channels, bias=False)
         self.reset_parameters()
 
     def reset_parameters(self):
         nn.init.xavier_uniform_(self.lin.weight)  # Glorot-uniform
 
+    def propagate_first(self) -> bool:
+        return self.order == "propagate_first" or (self.order == "auto" and self.in_channels < self.out_channels)
+
+    def product_width(self) -> int:
+        return self.in_channels if self.propagate_first() else self.out_channels
+
     def forward(self, x, edge_index):
+        if self.propagate_first():
+            return _fp32_linear(self.lin, super().forward(edge_index, x=x))
         x = _fp32_linear(self.lin, x)
         return super().forward(edge_index, x=x)
 
@@ -55,11 +71,11 @@ class CBMParallelMKLCSRSparseMatrixGCN(CBMCudaGCN):
 
 
 class CBMSequentialTorchCSRSparseMatrixGCN(CBMCudaGCN):
-    pass
+    two_step = True
 
 
 class CBMParallelTorchCSRSparseMatrixGCN(CBMCudaGCN):
-    pass
+    two_step = True
 
 
 class GCNModel(nn.Module):
@@ -72,6 +88,10 @@ class GCNModel(nn.Module):
         self.layers = nn.ModuleList(CBMCudaGCN(a, b, alpha=alpha) for a, b in zip(widths[:-1], widths[1:]))
         if structure is not None:
             self.share(structure)
+
+    def product_widths(self):
+        """Operand width of each layer's sparse product, in layer order."""
+        return [layer.product_width() for layer in self.layers]
 
     def share(self, structure):
         for layer in self.layers:

@@ -4,8 +4,9 @@ Mirrors gnns/message_passing/cbm_message_passing.py:7-107 of the reference: the 
 ``edge_index`` to ``[dst, src]``, builds the CBM structure once and caches it in ``cached_a_t``
 (assignable from outside, as benchmark/parallel/benchmark_gcn_cpu.py:62-66 does to share one
 structure between layers), and dispatches to the normalized or plain product.  The four reference
-class names are kept; they differ there only in which CPU kernel they call, so here they share one
-implementation on top of the CUDA products.  Unlike the reference, the output is a fresh tensor on
+class names are kept; there the ``MKL`` classes call the one-step product and the ``Torch`` classes
+the two-step path (``deltas @ x`` then the in-place update, cbm_message_passing.py:80-107), and the
+same distinction is kept here on the CUDA kernels (``two_step``).  Unlike the reference, the output is a fresh tensor on
 every call (the reference caches and aliases one output buffer, cbm_message_passing.py:26-29), and
 the product is differentiable with respect to ``x``.
 """
@@ -30,6 +31,8 @@ class CBMCudaMessagePassing(nn.Module):
         self.alpha = alpha
         self.cached_a_t = None
 
+    two_step = False  # True: delta product, then the update-only kernel
+
     def _structure(self, edge_index: torch.Tensor, dtype) -> cbm_matrix:
         if self.cached and self.cached_a_t is not None:
             return self.cached_a_t
@@ -44,7 +47,7 @@ class CBMCudaMessagePassing(nn.Module):
         if "x" not in kwargs:
             raise ValueError("x must be in kwargs")
         x = kwargs["x"]
-        return self._structure(edge_index, x.dtype).matmul(x)
+        return self._structure(edge_index, x.dtype).matmul(x, two_step=self.two_step)
 
 
 # Reference class names (cbm_message_passing.py:7, 39, 63, 90).
@@ -57,8 +60,8 @@ class CBMParallelMKLCSRSparseMatrixMessagePassing(CBMCudaMessagePassing):
 
 
 class CBMSequentialTorchCSRSparseMatrixMessagePassing(CBMCudaMessagePassing):
-    pass
+    two_step = True
 
 
 class CBMParallelTorchCSRSparseMatrixMessagePassing(CBMCudaMessagePassing):
-    pass
+    two_step = True

@@ -9,7 +9,11 @@ layer output, which is one all-gather of row shards.
 Vertices are relabelled so that each rank's rows are one contiguous block of ``shard_rows`` labels
 (the last labels of a block are padding when the rank owns fewer rows).  With equal blocks the
 all-gather is a single in-place ``all_gather_into_tensor`` over NCCL: every rank's kernel writes its
-finished rows straight into its slice of the gathered buffer.
+finished rows straight into its slice of the gathered buffer.  Where a product's output is what
+the next product gathers (or the model's output), the exchange can instead be done by the product
+kernel itself: every finished row is stored into the slice this shard occupies in every GPU's copy
+of the gathered buffer (peer memory reached by ordinary stores over NVLink), so the transfer runs
+while the product runs, followed by one barrier.
 """
 from __future__ import annotations
 
@@ -113,6 +117,7 @@ class ShardedCBM:
         self.device_index = device_index
         self._plan = None
         self._perm_t = None
+        self._host_bufs = {}
 
     @property
     def plan(self) -> _Plan:
@@ -140,17 +145,30 @@ class ShardedCBM:
     def from_labels(self, y: torch.Tensor) -> torch.Tensor:
         return y[self._perm(y.device)]
 
-    def local_product(self, x_labels: torch.Tensor, out_full: torch.Tensor) -> torch.Tensor:
-        """Compute this rank's rows into its slice of ``out_full`` ([n_labels, F]) and return the slice."""
+    def product_into(self, x_labels: torch.Tensor, y_shard: torch.Tensor, bcast=None, relu: bool = False) -> torch.Tensor:
+        """This rank's rows of the product into ``y_shard`` ([shard_rows, F], any row stride).
+        ``bcast``: device addresses (this GPU's or peers') of further buffers with ``y_shard``'s
+        layout that receive every finished row as it is produced, after a ReLU when ``relu``."""
         from . import _lib
         import ctypes
         f = x_labels.size(1)
-        mine = out_full[self.begin:self.end]
-        fn = _lib.lib().cbm_b200_fused_spmm_update if self.c.normalized else _lib.lib().cbm_b200_spmm_update
-        stream = torch.cuda.current_stream(x_labels.device).cuda_stream
-        _lib.check(fn(self.plan.handle, x_labels.data_ptr(), x_labels.stride(0), mine.data_ptr(),
-                      out_full.stride(0), f, ctypes.c_void_p(stream)))
-        return mine
+        L = _lib.lib()
+        stream = ctypes.c_void_p(torch.cuda.current_stream(x_labels.device).cuda_stream)
+        if bcast:
+            arr = (ctypes.c_void_p * len(bcast))(*bcast)
+            _lib.check(L.cbm_b200_spmm_update_bcast(self.plan.handle, x_labels.data_ptr(), x_labels.stride(0),
+                                                    y_shard.data_ptr(), y_shard.stride(0), f,
+                                                    1 if self.c.normalized else 0, 1 if relu else 0, len(bcast),
+                                                    arr, stream))
+        else:
+            fn = L.cbm_b200_fused_spmm_update if self.c.normalized else L.cbm_b200_spmm_update
+            _lib.check(fn(self.plan.handle, x_labels.data_ptr(), x_labels.stride(0), y_shard.data_ptr(),
+                          y_shard.stride(0), f, stream))
+        return y_shard
+
+    def local_product(self, x_labels: torch.Tensor, out_full: torch.Tensor) -> torch.Tensor:
+        """Compute this rank's rows into its slice of ``out_full`` ([n_labels, F]) and return the slice."""
+        return self.product_into(x_labels, out_full[self.begin:self.end])
 
     def matmul(self, x_labels: torch.Tensor, gather: bool = True) -> torch.Tensor:
         """``A @ x`` in label space: local subtrees, then (optionally) the all-gather of shards.
@@ -162,59 +180,240 @@ class ShardedCBM:
             dist.all_gather_into_tensor(out, mine, group=self.group)
         return out
 
+    def host_product(self, x_mine_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """The product for operands that live in host memory, one block of rows per rank.
+
+        ``x_mine_host``: this rank's block of the operand, [shard_rows, F] in label space (pinned
+        memory makes the copies asynchronous); ``y_host``: [shard_rows, F], receives this rank's
+        rows of the result.  Each rank sends only its own block over PCIe; one all-gather over
+        NVLink completes the operand on every GPU; then the product and the copy back.  Returns
+        when ``y_host`` is complete."""
+        import torch.distributed as dist
+        f = int(x_mine_host.size(1))
+        dev = torch.device("cuda", self.plan.device_index)
+        bufs = self._host_bufs.get(f)
+        if bufs is None:
+            bufs = (torch.zeros((self.part.n_labels, f), device=dev), torch.zeros((self.part.shard_rows, f), device=dev))
+            self._host_bufs = {f: bufs}
+        x_full, y_dev = bufs
+        mine = x_full[self.begin:self.end]
+        mine.copy_(x_mine_host, non_blocking=True)
+        if self.world > 1:
+            dist.all_gather_into_tensor(x_full, mine, group=self.group)
+        self.product_into(x_full, y_dev)
+        y_host.copy_(y_dev, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+
+
+class PeerBuffer:
+    """A [n_labels, width] buffer that exists at the same size on every rank with every rank's
+    copy mapped into every process (``torch.distributed._symmetric_memory``): the gathered layer
+    output that the product kernels of all GPUs write into directly."""
+
+    def __init__(self, n_labels: int, width: int, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.tensor = symm_mem.empty((n_labels, width), dtype=torch.float32, device=device)
+        self.tensor.zero_()
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.row_bytes = width * 4
+
+    def slice_addresses(self, first_row: int) -> list[int]:
+        """Device address of row ``first_row`` in every rank's copy (own copy included)."""
+        return [p + first_row * self.row_bytes for p in self.ptrs]
+
+    def barrier(self):
+        """All ranks' earlier stores into all copies are complete and visible after this."""
+        self.handle.barrier(channel=0)
+
 
 class ShardedGCN(torch.nn.Module):
     """Forward pass of a stack of GCN layers over a sharded CBM structure (weights replicated).
 
-    Per layer and rank: the dense map ``lin`` on the rank's own block of rows (1/world of the
-    GEMM), one in-place all-gather of the ``lin`` output shards (every rank needs all rows of the
-    product's right-hand side), then the product over the rank's subtrees.  ReLU between layers is
-    applied to the local block.  Everything lives in label space; padding rows are zero and stay
-    zero because the layers have no bias.
+    Per layer and rank, in the cheaper of two equivalent orders (``A (H W) = (A H) W``):
+    * "lin_first" (the reference's order, cbm_gcn.py:21-24; chosen when in >= out): the dense map
+      on the rank's own rows, an exchange of its output (every rank needs all rows of the
+      product's right-hand side), the product over the rank's subtrees;
+    * "propagate_first" (in < out): an exchange of the layer input, the product at the input
+      width, the dense map on the rank's own rows.
+    ReLU between layers acts on the local block.  ``exchange``: "nccl" = in-place
+    ``all_gather_into_tensor``; "peer" = where the exchanged tensor is a product's output (a
+    lin_first layer followed by a propagate_first layer, and the gathered model output) the
+    product kernel stores finished rows straight into every GPU's gathered buffer, ReLU applied
+    on the way, followed by one barrier; other exchanges stay on NCCL.
+    Everything lives in label space; padding rows are zero and stay zero (no bias).
     """
 
-    def __init__(self, widths, sharded: ShardedCBM):
+    def __init__(self, widths, sharded: ShardedCBM, exchange: str = "nccl"):
         super().__init__()
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
         self.sharded = sharded
+        self.exchange = exchange if sharded.world > 1 else "nccl"
         self._cache = {}
+        self._peer = {}
         self.lins = torch.nn.ModuleList(torch.nn.Linear(a, b, bias=False) for a, b in zip(widths[:-1], widths[1:]))
         for lin in self.lins:
             torch.nn.init.xavier_uniform_(lin.weight)
+        self.orders = ["propagate_first" if lin.in_features < lin.out_features else "lin_first" for lin in self.lins]
 
-    def _work_buffers(self, width: int, like: torch.Tensor):
-        """Two zero-initialised [n_labels, width] buffers per width, reused across calls: padding
-        rows are never written, so they stay zero."""
-        key = (width, like.device, like.dtype)
+    def _buffer(self, tag: str, width: int, like: torch.Tensor, rows: int | None = None):
+        """Zero-initialised work buffer, reused across calls (padding rows are never written, so
+        they stay zero)."""
+        rows = self.sharded.part.n_labels if rows is None else rows
+        key = (tag, width, rows, like.device)
         if key not in self._cache:
-            n = self.sharded.part.n_labels
-            self._cache[key] = (torch.zeros((n, width), dtype=like.dtype, device=like.device),
-                                torch.zeros((n, width), dtype=like.dtype, device=like.device))
+            self._cache[key] = torch.zeros((rows, width), dtype=torch.float32, device=like.device)
         return self._cache[key]
 
-    @torch.no_grad()
-    def forward(self, x_labels: torch.Tensor, gather_output: bool = True) -> torch.Tensor:
-        """``x_labels``: [n_labels, F_in] in label space.  Returns the output in label space
-        (all rows when ``gather_output``, else only this rank's block is meaningful).  The returned
-        tensor is a view of a buffer that the next call overwrites."""
+    def _peer_buffer(self, tag: str, width: int, like: torch.Tensor) -> PeerBuffer:
+        key = (tag, width)
+        if key not in self._peer:
+            self._peer[key] = PeerBuffer(self.sharded.part.n_labels, width, like.device, self.sharded.group)
+        return self._peer[key]
+
+    @staticmethod
+    def _mm(h, lin, out):
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False  # full fp32, as the 1e-4 tolerance needs
+        try:
+            torch.mm(h, lin.weight.t(), out=out)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+
+    def _gather(self, full, mine):
         import torch.distributed as dist
+        if self.sharded.world > 1:
+            dist.all_gather_into_tensor(full, mine, group=self.sharded.group)
+
+    @torch.no_grad()
+    def forward(self, x_labels: torch.Tensor, gather_output: bool = True, probe: dict | None = None) -> torch.Tensor:
+        """``x_labels``: [n_labels, F_in] in label space, all rows present on every rank.  Returns
+        the output in label space (all rows when ``gather_output``, else only this rank's block is
+        meaningful).  The returned tensor is a view of a buffer that the next call overwrites.
+        ``probe`` (a dict) receives per-layer phase times in ms and the last product's operands."""
         sh = self.sharded
-        h_local = x_labels[sh.begin:sh.end]
-        out = None
+        n_layers = len(self.lins)
+        timing = probe is not None
+
+        def tick():
+            if not timing:
+                return None
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            return e
+
+        phases = []
+        h_full = x_labels                      # all rows of the current layer input, or None
+        h_local = x_labels[sh.begin:sh.end]    # this rank's rows of it
+        y_full = None
         for i, lin in enumerate(self.lins):
-            if i:
-                h_local = h_local.relu()
-            f = lin.out_features
-            fp = -(-f // 4) * 4  # widths are padded to a multiple of 4 floats for the 128-bit path
-            z, out = self._work_buffers(fp, x_labels)
-            prev = torch.backends.cuda.matmul.allow_tf32
-            torch.backends.cuda.matmul.allow_tf32 = False  # full fp32, as the 1e-4 tolerance needs
-            try:
-                torch.mm(h_local[:, :lin.in_features], lin.weight.t(), out=z[sh.begin:sh.end, :f])
-            finally:
-                torch.backends.cuda.matmul.allow_tf32 = prev
-            if sh.world > 1:
-                dist.all_gather_into_tensor(z, z[sh.begin:sh.end], group=sh.group)
-            h_local = sh.local_product(z, out)
-        if gather_output and sh.world > 1:
-            dist.all_gather_into_tensor(out, h_local, group=sh.group)
-        return out[:, :self.lins[-1].out_features]
+            a, b = lin.in_features, lin.out_features
+            bp = -(-b // 4) * 4
+            last = i == n_layers - 1
+            # will whoever consumes this layer's output need all rows of it on every rank?
+            next_gathers = (not last and self.orders[i + 1] == "propagate_first") or (last and gather_output)
+            y_full = self._buffer("y%d" % i, bp, x_labels)
+            y_local = y_full[sh.begin:sh.end]
+            delivered = False
+            t0 = tick()
+            if self.orders[i] == "propagate_first":
+                ap = -(-a // 4) * 4
+                if h_full is None:
+                    h_full = self._buffer("hin%d" % i, ap, x_labels)
+                    mine = h_full[sh.begin:sh.end]
+                    mine[:, :a].copy_(h_local[:, :a])
+                    self._gather(h_full, mine)
+                elif h_full.size(1) != ap or h_full.stride(0) % 4:
+                    padded = self._buffer("hpad%d" % i, ap, x_labels)
+                    padded[:, :a].copy_(h_full[:, :a])
+                    h_full = padded
+                t1 = tick()
+                p_local = self._buffer("p%d" % i, ap, x_labels, rows=sh.part.shard_rows)
+                sh.product_into(h_full, p_local)
+                t2 = tick()
+                self._mm(p_local[:, :a], lin, y_local[:, :b])
+                if not last:
+                    y_local.relu_()
+                t3 = tick()
+                kinds, prod = ("exchange", "product", "dense"), (h_full, p_local, ap)
+            else:
+                z_full = self._buffer("z%d" % i, bp, x_labels)
+                self._mm(h_local[:, :a], lin, z_full[sh.begin:sh.end, :b])
+                t1 = tick()
+                self._gather(z_full, z_full[sh.begin:sh.end])
+                t2 = tick()
+                if next_gathers and self.exchange == "peer":
+                    # the product's output is what gets exchanged next: the kernel delivers it
+                    pb = self._peer_buffer("g%d" % i, bp, x_labels)
+                    pb.barrier()                       # every rank is done reading the previous contents
+                    raw = self._buffer("raw%d" % i, bp, x_labels, rows=sh.part.shard_rows)
+                    sh.product_into(z_full, raw, bcast=pb.slice_addresses(sh.begin), relu=not last)
+                    pb.barrier()
+                    y_full, y_local, delivered = pb.tensor, pb.tensor[sh.begin:sh.end], True
+                    prod = (z_full, raw if last else None, bp)
+                else:
+                    sh.product_into(z_full, y_local)
+                    prod = (z_full, y_local.clone() if (timing and last) else None, bp)
+                    if not last:
+                        y_local.relu_()
+                t3 = tick()
+                kinds = ("dense", "exchange", "product")
+            if timing:
+                phases.append(dict(order=self.orders[i], product_width=prod[2], exchange_width=prod[2],
+                                   ev=(t0, t1, t2, t3), kinds=kinds))
+                if last:
+                    probe["last_product"] = prod
+            h_local, h_full = y_local, None
+            if delivered:
+                h_full = y_full
+            elif next_gathers:
+                self._gather(y_full, y_local)
+                h_full = y_full
+        if timing:
+            torch.cuda.synchronize()
+            rows = []
+            for ph in phases:
+                t = ph.pop("ev")
+                kinds = ph.pop("kinds")
+                d = dict(ph, product_ms=0.0, exchange_ms=0.0, dense_ms=0.0)
+                for k, (e0, e1) in zip(kinds, zip(t[:-1], t[1:])):
+                    d[k + "_ms"] = e0.elapsed_time(e1)
+                rows.append(d)
+            probe["phases"] = rows
+        return y_full[:, :self.lins[-1].out_features]
+
+    def timed_forward(self, x_labels: torch.Tensor) -> list[dict]:
+        """One forward pass with device timestamps between the phases of every layer.  In a
+        lin_first layer delivered by the product kernel ("peer"), the exchange of its output is
+        inside ``product_ms``."""
+        probe: dict = {}
+        self.forward(x_labels, gather_output=False, probe=probe)
+        return probe["phases"]
+
+    def check_last_product(self, x_labels: torch.Tensor, rows: int = 500) -> dict:
+        """Sampled rows this rank owns of the LAST layer's sparse product, given the operand the
+        model itself fed it, against a float64 CSR product on the host."""
+        sh, c = self.sharded, self.sharded.c
+        probe: dict = {}
+        self.forward(x_labels, gather_output=False, probe=probe)
+        operand, result, width = probe["last_product"]
+        lab = sh.part.perm
+        own = np.nonzero((lab >= sh.begin) & (lab < sh.end))[0]
+        pick = np.sort(np.random.default_rng(77 + sh.rank).choice(own, min(rows, own.size), replace=False))
+        x_vertex = operand[sh._perm(operand.device)].cpu().numpy().astype(np.float64)   # label -> vertex order
+        got = result[torch.from_numpy((lab[pick] - sh.begin).astype(np.int64)).to(result.device)].cpu().numpy()
+        keep = np.isin(c._row, pick)
+        import scipy.sparse as sp
+        n = c.num_rows
+        sub = sp.csr_matrix((np.ones(int(keep.sum())), (c._row[keep], c._col[keep])), shape=(n, n))[pick]
+        if c.col_multiplier is not None:
+            s = c.col_multiplier.numpy().astype(np.float64)
+            sub = sp.diags(s[pick]) @ sub @ sp.diags(s)
+        want = np.asarray(sub @ x_vertex)
+        d = np.abs(got.astype(np.float64) - want)
+        return dict(rows=int(pick.size), max_abs_err=float(d.max()),
+                    max_rel_err=float(d.max() / max(1e-30, np.abs(want).max())),
+                    max_err_over_tol=float((d / (1e-4 + 1e-4 * np.abs(want))).max()))

@@ -167,6 +167,28 @@ int cbm_b200_csr_spmm(int32_t n_rows, const int32_t* row_b, const int32_t* row_e
                       const int32_t* col, const float* val, const float* x, int64_t ldx, float* y,
                       int64_t ldy, int32_t f, void* stream);
 
+/* The same product from a reusable plan: the counterpart of the oneMKL handle the reference
+ * creates from these arrays before every product (mkl_sparse_s_create_csr,
+ * cbm/cbm_extensions.cpp:1726-1734).  crow (n_rows + 1 entries), col, val are [host]; the plan
+ * keeps its own device copy.  Long rows are cut into segments and balanced over the GPU like the
+ * rows of a CBM structure, which the array form above (one warp per whole row) does not do.
+ * y = M x is then cbm_b200_spmm_update(plan, x, ...) with x of n_cols rows and y of n_rows rows. */
+int cbm_b200_csr_plan_create(int32_t n_rows, int32_t n_cols, const int32_t* crow, const int32_t* col,
+                             const float* val, int32_t device, cbm_b200_plan** out);
+
+/* Multi-GPU form of the two fused products (no counterpart in the reference, which has no
+ * distributed code): every finished row is written to y as usual and, after an optional ReLU,
+ * to n_dst further buffers dst[k] [dev, possibly memory of a peer GPU mapped into this process]
+ * with y's layout and leading dimension — the place this shard occupies in each GPU's copy of
+ * the gathered layer output.  The stores to peers are ordinary stores issued by the product
+ * kernel as rows finish, so the exchange overlaps the product; the caller synchronises the GPUs
+ * afterwards.  y always receives the rows without the ReLU (children in the tree read them).
+ * At most CBM_B200_MAX_BCAST destinations. */
+#define CBM_B200_MAX_BCAST 8
+int cbm_b200_spmm_update_bcast(cbm_b200_plan* p, const float* x, int64_t ldx, float* y, int64_t ldy,
+                               int32_t f, int32_t normalized, int32_t relu, int32_t n_dst,
+                               float* const* dst, void* stream);
+
 /* Host-buffer forms of the two fused products: x [host] n_labels x f and y [host]
  * (own_end-own_begin) x f, both contiguous (ld = f).  The call copies x to the device, runs the product and copies y back on the
  * plan's own stream, and returns when y is complete.  Staging buffers belong to the plan and grow
@@ -180,6 +202,11 @@ int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float* y, int32_
  * CBM_B200_ERR_TIMEOUT when the wait gave up as designed, any other status is a failure.  The
  * context stays usable. */
 int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* stream);
+
+/* Measurement aid (no counterpart in the reference): GB/s at which all SMs of `device` together
+ * stream a 32 MB buffer that stays resident in L2 — the ceiling of the gather traffic of the
+ * product kernels.  Allocates and frees its buffer; returns a negative number on failure. */
+double cbm_b200_probe_l2_read_gbps(int32_t device);
 
 /* --------------------------------------------------------------------------------------------
  * The fused product for callers that must not allocate.  (No counterpart in the reference, whose

@@ -32,13 +32,33 @@ def _worker(rank, world, port, q):
         y = sh.from_labels(sh.matmul(xl)).cpu().numpy()
         sh.plan.status()
         err = float(np.abs(y - sparse_product(ei.numpy(), x, True)).max())
-        torch.manual_seed(0)
-        model = ShardedGCN((100, 256, 47), sh).cuda()
-        out = sh.from_labels(model(xl)).cpu().numpy()
-        w1, w2 = (l.weight.detach().cpu().numpy().astype(np.float64) for l in model.lins)
-        h = np.maximum(sparse_product(ei.numpy(), (x @ w1.T).astype(np.float32), True), 0)
-        ref = sparse_product(ei.numpy(), (h @ w2.T).astype(np.float32), True)
-        q.put((rank, err, float(np.abs(out - ref).max() / max(1.0, np.abs(ref).max()))))
+        err2 = 0.0
+        # (100,256,47): propagate_first then lin_first; (100,64,96,47): lin_first -> propagate_first
+        # -> lin_first, so with exchange="peer" one hand-over between layers and the model output
+        # are delivered by the product kernel's stores into the peers' gathered buffers
+        for widths, exchange in (((100, 256, 47), "nccl"), ((100, 256, 47), "peer"), ((100, 64, 96, 47), "nccl"),
+                                 ((100, 64, 96, 47), "peer")):
+            torch.manual_seed(0)
+            model = ShardedGCN(widths, sh, exchange=exchange).cuda()
+            h = x.astype(np.float64)
+            for k, l in enumerate(model.lins):
+                w = l.weight.detach().cpu().numpy().astype(np.float64)
+                h = sparse_product(ei.numpy(), (h @ w.T).astype(np.float32), True)
+                if k < len(model.lins) - 1:
+                    h = np.maximum(h, 0)
+            for _ in range(2):  # buffers are reused between calls
+                out = sh.from_labels(model(xl)).cpu().numpy()
+            err2 = max(err2, float(np.abs(out - h).max() / max(1.0, np.abs(h).max())))
+            par = model.check_last_product(xl, rows=200)
+            err2 = max(err2, par["max_err_over_tol"] * 1e-4)
+            assert len(model.timed_forward(xl)) == len(widths) - 1
+        # operands in host memory: own block over PCIe, all-gather over NVLink, product, copy back
+        xh = xl.cpu().pin_memory()
+        yh = torch.empty((sh.part.shard_rows, 100)).pin_memory()
+        sh.host_product(xh[sh.begin:sh.end], yh)
+        full = sh.matmul(xl)
+        assert torch.equal(yh, full[sh.begin:sh.end].cpu())
+        q.put((rank, err, err2))
     finally:
         dist.destroy_process_group()
 

@@ -419,3 +419,73 @@ def test_alpha_search_measures_on_the_gpu():
     y = torch.empty((n, 64), device="cuda")
     c.omp_mkl_csr_fused_spmm_update(_dev(x), y)
     np.testing.assert_allclose(y.cpu().numpy(), sparse_product(ei_np, x, True), **TOL)
+
+
+def test_csr_plan_balances_long_rows_and_matches_the_array_form():
+    """Plain CSR through a plan (every row a child of the virtual root, long rows cut into
+    segments) against the array form and float64, on a matrix with one 30 000-entry row,
+    rectangular, arbitrary values."""
+    from cbm4gnn_b200.cbm import csr_matrix_plan
+    import scipy.sparse as sp
+    rng = np.random.default_rng(21)
+    n_rows, n_cols = 5000, 30000
+    dense_row = np.stack([np.zeros(n_cols, dtype=np.int64), np.arange(n_cols)])
+    rest = np.stack([rng.integers(1, n_rows, 60000), rng.integers(0, n_cols, 60000)])
+    ij = np.concatenate([dense_row, rest], axis=1)
+    a = sp.csr_matrix((rng.standard_normal(ij.shape[1]).astype(np.float32), (ij[0], ij[1])), shape=(n_rows, n_cols))
+    a.sum_duplicates()
+    a.sort_indices()
+    plan = csr_matrix_plan(a.indptr, a.indices, a.data, n_cols)
+    for f in (128, 47):
+        x = rng.standard_normal((n_cols, f)).astype(np.float32)
+        y = plan.matmul(_dev(x))
+        plan.status()
+        want = a.astype(np.float64) @ x.astype(np.float64)
+        np.testing.assert_allclose(y.cpu().numpy(), want, atol=2e-3, rtol=1e-4)  # 30 000-term fp32 sums
+        np.testing.assert_allclose(y.cpu().numpy()[1:], want[1:], **TOL)
+    with pytest.raises(RuntimeError, match="shape mismatch"):
+        plan.matmul(torch.zeros((n_cols + 1, 8), device="cuda"))
+
+
+def test_broadcast_epilogue_writes_every_destination(c1):
+    """The multi-GPU form of the product on one GPU: finished rows go to y and, after the ReLU,
+    to further buffers with y's layout (on several GPUs these are the peers' gathered buffers)."""
+    ei, _ = c1
+    eil = with_self_loops(ei)
+    c = _cbm(eil, 2, normalized=True)
+    n = c.num_rows
+    L = _lib.lib()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for f, ld in ((500, 500), (64, 64), (47, 47), (128, 160)):
+        x = torch.randn((n, f), device="cuda")
+        want = torch.empty((n, f), device="cuda")
+        c.omp_mkl_csr_fused_spmm_update(x, want)
+        y = torch.full((n, ld), float("nan"), device="cuda")
+        dst = [torch.full((n, ld), float("nan"), device="cuda") for _ in range(3)]
+        arr = (ctypes.c_void_p * 3)(*[d.data_ptr() for d in dst])
+        _lib.check(L.cbm_b200_spmm_update_bcast(c.plan().handle, x.data_ptr(), f, y.data_ptr(), ld, f, 1, 1, 3, arr, st))
+        c.plan().status()
+        assert torch.equal(y[:, :f], want)                     # the tree's own copy: no ReLU
+        for d in dst:
+            assert torch.equal(d[:, :f], want.relu())
+            assert torch.isnan(d[:, f:]).all()                 # nothing outside the rows' width
+    assert L.cbm_b200_spmm_update_bcast(c.plan().handle, x.data_ptr(), f, y.data_ptr(), ld, f, 1, 0, 9, arr, st) == 1
+
+
+def test_host_operands_with_ragged_width(c1):
+    """Host tensors whose width is not a multiple of 4 (the 47-wide output layer of the fifth
+    configuration): the staged product equals the device-resident one exactly."""
+    ei, c = c1
+    n = c.num_rows
+    for f in (47, 131, 5, 3):
+        x = torch.randn((n, f))
+        want = torch.empty((n, f), device="cuda")
+        c.omp_mkl_csr_spmm_update(x.cuda(), want)
+        got = torch.empty((n, f))
+        c.omp_mkl_csr_spmm_update(x, got)
+        assert torch.equal(got, want.cpu())
+
+
+def test_l2_probe_reports_a_plausible_rate():
+    r = _lib.lib().cbm_b200_probe_l2_read_gbps(torch.cuda.current_device())
+    assert 2000.0 < r < 60000.0

@@ -42,16 +42,15 @@ def test_partition_owns_whole_subtrees_and_balances(world):
 class _OracleShard(ShardedCBM):
     """Per-rank product through the CPU restatement instead of a CUDA plan."""
 
-    def local_product(self, x_labels, out_full):
+    def product_into(self, x_labels, y_shard, bcast=None, relu=False):
         c = self.c
         x = x_labels[torch.from_numpy(self.part.perm.astype(np.int64))].numpy()   # back to vertex order
         y = orc.fused_spmm_update(c.mst_row.numpy(), c.mst_col.numpy(), c._crow, c._dcol, c._dval,
                                   c.col_multiplier.numpy(), np.ascontiguousarray(x), parallel=False)
-        mine = out_full[self.begin:self.end]
         lab = self.part.perm
         own = (lab >= self.begin) & (lab < self.end)
-        mine[torch.from_numpy(lab[own] - self.begin).long()] = torch.from_numpy(y[own])
-        return mine
+        y_shard[torch.from_numpy(lab[own] - self.begin).long()] = torch.from_numpy(y[own])
+        return y_shard
 
 
 def _worker(rank, world, port, fail_rank, q):
@@ -67,13 +66,26 @@ def _worker(rank, world, port, fail_rank, q):
         y = sh.from_labels(sh.matmul(xl)).numpy()
         err = float(np.abs(y - sparse_product(ei.numpy(), x, True)).max())
         # two stacked layers in label space equal the unsharded computation
-        torch.manual_seed(0)
-        model = ShardedGCN((12, 16, 5), sh)
-        out = sh.from_labels(model(xl)).numpy()
-        w1, w2 = (l.weight.detach().numpy().astype(np.float64) for l in model.lins)
-        h = np.maximum(sparse_product(ei.numpy(), (x @ w1.T).astype(np.float32), True), 0)
-        ref = sparse_product(ei.numpy(), (h @ w2.T).astype(np.float32), True)
-        q.put((rank, err, float(np.abs(out - ref).max())))
+        # widths chosen so that both layer orders and both hand-overs between them occur:
+        # (12,16,5) = propagate_first then lin_first, (12,8,10,10) = lin_first, propagate_first, lin_first
+        err2 = 0.0
+        for widths in ((12, 16, 5), (12, 8, 10, 10)):
+            torch.manual_seed(0)
+            model = ShardedGCN(widths, sh)
+            assert model.orders == ["propagate_first" if a < b else "lin_first" for a, b in zip(widths[:-1], widths[1:])]
+            out = sh.from_labels(model(xl)).numpy()
+            h = x
+            for k, l in enumerate(model.lins):
+                w = l.weight.detach().numpy().astype(np.float64)
+                h = sparse_product(ei.numpy(), (h @ w.T).astype(np.float32), True)
+                if k < len(model.lins) - 1:
+                    h = np.maximum(h, 0)
+            err2 = max(err2, float(np.abs(out - h).max()))
+            # without the final gather the rank's own block is still right
+            own = (sh.part.perm >= sh.begin) & (sh.part.perm < sh.end)
+            loc = sh.from_labels(model(xl, gather_output=False)).numpy()
+            err2 = max(err2, float(np.abs(loc[own] - h[own]).max()))
+        q.put((rank, err, err2))
     finally:
         dist.destroy_process_group()
 

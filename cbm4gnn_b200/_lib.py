@@ -22,11 +22,30 @@ LIB_PATH = os.path.join(_PKG_DIR, "libcbm_b200.so")
 SOURCES = [
     os.path.join(_PKG_DIR, "csrc", "cbm_engine.cu"),
     os.path.join(_PKG_DIR, "csrc", "cbm_builder.cpp"),
+    os.path.join(_PKG_DIR, "csrc", "cbm_dense.cu"),
 ]
 HEADERS = [
     os.path.join(_ROOT, "include", "cbm_b200.h"),
     os.path.join(_PKG_DIR, "csrc", "cbm_common.h"),
 ]
+_OBJ_DIR = os.path.join(_PKG_DIR, "build")
+
+
+def _cutlass_includes() -> list[str]:
+    """Header trees of CUTLASS / CuTe (the dense maps instantiate their sm100 templates): the
+    environment variable CUTLASS_HOME, else the copy vendored inside the flashinfer package."""
+    roots = [os.environ.get("CUTLASS_HOME")]
+    try:
+        import importlib.util
+        spec = importlib.util.find_spec("flashinfer")
+        if spec and spec.submodule_search_locations:
+            roots.append(os.path.join(list(spec.submodule_search_locations)[0], "data", "cutlass"))
+    except Exception:
+        pass
+    for r in roots:
+        if r and os.path.exists(os.path.join(r, "include", "cutlass", "cutlass.h")):
+            return [os.path.join(r, "include"), os.path.join(r, "tools", "util", "include")]
+    raise RuntimeError("CUTLASS headers not found: set CUTLASS_HOME (needed to compile csrc/cbm_dense.cu)")
 
 # Every symbol include/cbm_b200.h declares; the CPU test-suite checks the library exports all of them.
 EXPORTED = [
@@ -52,6 +71,10 @@ EXPORTED = [
     "cbm_b200_csr_plan_create",
     "cbm_b200_spmm_update_bcast",
     "cbm_b200_probe_l2_read_gbps",
+    "cbm_b200_dense_forward",
+    "cbm_b200_dense_grad_input",
+    "cbm_b200_dense_grad_weight",
+    "cbm_b200_dense_grad_weight_workspace",
     "cbm_b200_spmm_update_host",
     "cbm_b200_spmm_update_static",
     "cbm_b200_selftest_wait",
@@ -73,26 +96,43 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library for sm_100a next to this file and return its path."""
+    """Compile the library for sm_100a next to this file and return its path.  Every source is
+    compiled to its own object (kept under ``build/``, so that touching the engine does not
+    recompile the CUTLASS instantiations, which take over a minute) and the objects are linked."""
     if not force and not needs_build():
         return LIB_PATH
-    cmd = [
-        _nvcc(), "-O3", "-std=c++17",
-        "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-        "-Xcompiler", "-fPIC,-fopenmp,-O3",
-        "-shared",
-        "-I", os.path.join(_ROOT, "include"),
-        "-I", os.path.join(_PKG_DIR, "csrc"),
-        "-o", LIB_PATH, *SOURCES, "-lgomp",
-    ]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
+    os.makedirs(_OBJ_DIR, exist_ok=True)
+    newest_header = max(os.path.getmtime(h) for h in HEADERS)
+    objs, log = [], []
+    for src in SOURCES:
+        obj = os.path.join(_OBJ_DIR, os.path.splitext(os.path.basename(src))[0] + ".o")
+        objs.append(obj)
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), newest_header):
+            continue
+        cmd = [
+            _nvcc(), "-O3", "-std=c++17",
+            "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+            "-Xcompiler", "-fPIC,-fopenmp,-O3",
+            "-I", os.path.join(_ROOT, "include"),
+            "-I", os.path.join(_PKG_DIR, "csrc"),
+        ]
+        if src.endswith("cbm_dense.cu"):
+            cmd += ["--expt-relaxed-constexpr", "-diag-suppress", "20012"]
+            for inc in _cutlass_includes():
+                cmd += ["-I", inc]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+        cmd += ["-c", src, "-o", obj]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        log.append(res.stderr)
+    cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB_PATH, *objs, "-lgomp"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        raise RuntimeError("link failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
     if verbose:
-        print(res.stderr)
+        print("".join(log))
     return LIB_PATH
 
 
@@ -144,6 +184,11 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_spmm_update_bcast", c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32,
         c_int32, c_int32, POINTER(c_void_p), c_void_p)
     sig("cbm_b200_probe_l2_read_gbps", c_double, c_int32)
+    for name in ("cbm_b200_dense_forward", "cbm_b200_dense_grad_input"):
+        sig(name, c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p)
+    sig("cbm_b200_dense_grad_weight", c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32,
+        c_int32, c_int32, c_void_p, c_int64, c_void_p)
+    sig("cbm_b200_dense_grad_weight_workspace", c_int64, c_int32, c_int32, c_int32)
     sig("cbm_b200_spmm_update_host", c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32)
     sig("cbm_b200_spmm_update_static", c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32,
         c_int32, c_void_p)

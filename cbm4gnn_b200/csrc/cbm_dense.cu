@@ -1,0 +1,177 @@
+// Dense maps of the GCN layers on the 5th-generation tensor cores (sm_100a).
+//
+// A GCN layer of the reference is `lin` followed by `propagate`
+// (gnns/graph_convolutional_network/cbm_gcn.py:21-24): a bias-free [N,in] x [in,out] map in fp32.
+// The sparse half runs in cbm_engine.cu; this file is the dense half and its two gradients
+//     forward   Y  = X  W^T      X [N,in],   W [out,in]          -> Y  [N,out]
+//     input     dX = dY W        dY [N,out], W [out,in]          -> dX [N,in]
+//     weight    dW = dY^T X      dY [N,out], X [N,in]            -> dW [out,in]
+// as fp32-accurate GEMMs on tcgen05: every fp32 operand is split on the fly into three bf16 terms
+// (x = b0 + b1 + b2 with 8 mantissa bits each), the products of the terms that matter are issued as
+// bf16 UMMA instructions with TMA-staged operands and accumulated in fp32 in tensor memory.  The
+// result carries fp32 accuracy (error ~2^-22 relative per product), which the 1e-4 tolerance of the
+// reference's tests needs and single-pass TF32/BF16 does not give.
+//
+// The kernels are instantiations of the CUTLASS sm100 collective builders (TMA loads without
+// cluster multicast — cluster shape 1x1x1 —, an input-transform warp group, tcgen05.mma with the
+// accumulator in TMEM, TMA-store epilogue).  The weight gradient contracts over the N rows of the
+// graph (hundreds of thousands) into a tiny [out,in] result, so it runs as a batched GEMM over row
+// chunks followed by a reduction of the partial results in a fixed order.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <string>
+
+#include "cutlass/cutlass.h"
+#include "cute/tensor.hpp"
+#include "cutlass/epilogue/collective/collective_builder.hpp"
+#include "cutlass/gemm/collective/collective_builder.hpp"
+#include "cutlass/gemm/device/gemm_universal_adapter.h"
+#include "cutlass/gemm/kernel/gemm_universal.hpp"
+#include "cutlass/util/packed_stride.hpp"
+
+#include "cbm_b200.h"
+#include "cbm_common.h"
+
+namespace cbm_dense {
+
+using namespace cute;
+using RowMajor = cutlass::layout::RowMajor;
+using ColMajor = cutlass::layout::ColumnMajor;
+
+// D[M,N] = A[M,K] * B[K,N], fp32 in and out, row-major D.
+template <class LayoutA, class LayoutB, int TileN>
+struct FastGemm {
+    using TileShape = Shape<_128, Int<TileN>, _16>;
+    using ClusterShape = Shape<_1, _1, _1>;
+    using CollectiveEpilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, TileShape, ClusterShape,
+        cutlass::epilogue::collective::EpilogueTileAuto, float, float, float, RowMajor, 4, float, RowMajor, 4,
+        cutlass::epilogue::TmaWarpSpecialized1Sm>::CollectiveOp;
+    using CollectiveMainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, float, TileShape,
+        ClusterShape,
+        cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename CollectiveEpilogue::SharedStorage))>,
+        cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32SmemSm100>::CollectiveOp;
+    using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, CollectiveMainloop, CollectiveEpilogue, void>;
+    using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
+    using StrideA = typename Kernel::StrideA;
+    using StrideB = typename Kernel::StrideB;
+    using StrideD = typename Kernel::StrideD;
+};
+
+template <class G>
+int run_gemm(const char* who, int m, int n, int k, int batch, const float* a, int64_t lda, int64_t batch_a,
+             const float* b, int64_t ldb, int64_t batch_b, float* d, int64_t ldd, int64_t batch_d, void* workspace,
+             size_t workspace_bytes, cudaStream_t stream) {
+    typename G::StrideA sa{};
+    typename G::StrideB sb{};
+    typename G::StrideD sd{};
+    // the leading dimension sits in the non-unit mode of each stride, the batch stride in the last
+    if constexpr (is_static_v<remove_cvref_t<decltype(get<0>(sa))>>) {
+        get<1>(sa) = lda;  // A stored with M contiguous (column-major)
+    } else {
+        get<0>(sa) = lda;  // K contiguous (row-major)
+    }
+    if constexpr (is_static_v<remove_cvref_t<decltype(get<0>(sb))>>) {
+        get<1>(sb) = ldb;  // N contiguous
+    } else {
+        get<0>(sb) = ldb;  // K contiguous
+    }
+    get<0>(sd) = ldd;
+    get<2>(sa) = batch_a;
+    get<2>(sb) = batch_b;
+    get<2>(sd) = batch_d;
+    typename G::Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm,
+                                     {m, n, k, batch},
+                                     {a, sa, b, sb},
+                                     {{1.0f, 0.0f}, nullptr, sd, d, sd}};
+    typename G::Gemm gemm;
+    if (gemm.can_implement(args) != cutlass::Status::kSuccess)
+        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": shape or alignment not supported (widths and leading "
+                                                              "dimensions must be multiples of 4 floats, pointers 16-byte aligned)");
+    if (G::Gemm::get_workspace_size(args) > workspace_bytes)
+        return cbm::fail(CBM_B200_ERR_ALLOC, std::string(who) + ": workspace too small");
+    cutlass::Status st = gemm.initialize(args, workspace, stream);
+    if (st == cutlass::Status::kSuccess) st = gemm.run(stream);
+    if (st != cutlass::Status::kSuccess)
+        return cbm::fail(CBM_B200_ERR_CUDA, std::string(who) + ": " + cutlassGetStatusString(st));
+    return CBM_B200_OK;
+}
+
+// fixed-order sum of `parts` partial [rows, cols] results (each a contiguous block) into out
+__global__ void reduce_partials_kernel(const float* __restrict__ part, int parts, int64_t block, float* __restrict__ out,
+                                       int rows, int cols, int64_t ldo) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)rows * cols) return;
+    float s = 0.f;
+    for (int p = 0; p < parts; ++p) s += part[(int64_t)p * block + i];
+    out[(i / cols) * ldo + (i % cols)] = s;
+}
+
+using GemmNT = FastGemm<RowMajor, ColMajor, 128>;  // A K-contiguous, B K-contiguous: X W^T
+using GemmNN = FastGemm<RowMajor, RowMajor, 128>;  // A K-contiguous, B N-contiguous: dY W
+using GemmTN = FastGemm<ColMajor, RowMajor, 128>;  // A M-contiguous, B N-contiguous: dY^T X
+
+}  // namespace cbm_dense
+
+using namespace cbm_dense;
+
+extern "C" int cbm_b200_dense_forward(const float* x, int64_t ldx, const float* w, int64_t ldw, float* y, int64_t ldy,
+                                      int32_t n_rows, int32_t n_in, int32_t n_out, void* stream) {
+    if (!x || !w || !y || n_rows < 0 || n_in <= 0 || n_out <= 0)
+        return cbm::fail(CBM_B200_ERR_ARG, "dense_forward: bad arguments");
+    if (n_rows == 0) return CBM_B200_OK;
+    return run_gemm<GemmNT>("dense_forward", n_rows, n_out, n_in, 1, x, ldx, 0, w, ldw, 0, y, ldy, 0, nullptr, 0,
+                            (cudaStream_t)stream);
+}
+
+extern "C" int cbm_b200_dense_grad_input(const float* dy, int64_t lddy, const float* w, int64_t ldw, float* dx,
+                                         int64_t lddx, int32_t n_rows, int32_t n_in, int32_t n_out, void* stream) {
+    if (!dy || !w || !dx || n_rows < 0 || n_in <= 0 || n_out <= 0)
+        return cbm::fail(CBM_B200_ERR_ARG, "dense_grad_input: bad arguments");
+    if (n_rows == 0) return CBM_B200_OK;
+    return run_gemm<GemmNN>("dense_grad_input", n_rows, n_in, n_out, 1, dy, lddy, 0, w, ldw, 0, dx, lddx, 0, nullptr, 0,
+                            (cudaStream_t)stream);
+}
+
+extern "C" int64_t cbm_b200_dense_grad_weight_workspace(int32_t n_rows, int32_t n_in, int32_t n_out) {
+    const int64_t chunks = std::max<int64_t>(1, std::min<int64_t>(CBM_B200_DENSE_MAX_CHUNKS, ((int64_t)n_rows + 2047) / 2048));
+    return chunks * (int64_t)n_in * n_out * (int64_t)sizeof(float);
+}
+
+extern "C" int cbm_b200_dense_grad_weight(const float* dy, int64_t lddy, const float* x, int64_t ldx, float* dw,
+                                          int64_t lddw, int32_t n_rows, int32_t n_in, int32_t n_out, void* workspace,
+                                          int64_t workspace_bytes, void* stream) {
+    if (!dy || !x || !dw || n_rows < 0 || n_in <= 0 || n_out <= 0)
+        return cbm::fail(CBM_B200_ERR_ARG, "dense_grad_weight: bad arguments");
+    cudaStream_t s = (cudaStream_t)stream;
+    // rows are cut into equal chunks (a multiple of 16 rows, the K tile) contracted independently;
+    // the tail that does not fill a chunk is one more, shorter product
+    const int64_t chunks = std::max<int64_t>(1, std::min<int64_t>(CBM_B200_DENSE_MAX_CHUNKS, ((int64_t)n_rows + 2047) / 2048));
+    const int64_t need = cbm_b200_dense_grad_weight_workspace(n_rows, n_in, n_out) + (int64_t)n_in * n_out * 4;
+    if (!workspace || workspace_bytes < need)
+        return cbm::fail(CBM_B200_ERR_ARG, "dense_grad_weight: workspace of " + std::to_string(need) + " bytes needed");
+    float* part = static_cast<float*>(workspace);
+    const int64_t block = (int64_t)n_in * n_out;
+    int64_t rows_per = (n_rows / chunks) / 16 * 16;
+    int parts = 0;
+    if (rows_per > 0) {
+        int rc = run_gemm<GemmTN>("dense_grad_weight", n_out, n_in, (int)rows_per, (int)chunks, dy, lddy, rows_per * lddy, x,
+                                  ldx, rows_per * ldx, part, n_in, block, nullptr, 0, s);
+        if (rc) return rc;
+        parts = (int)chunks;
+    }
+    const int64_t done = rows_per * (rows_per > 0 ? chunks : 0);
+    if (done < n_rows) {
+        int rc = run_gemm<GemmTN>("dense_grad_weight", n_out, n_in, (int)(n_rows - done), 1, dy + done * lddy, lddy, 0,
+                                  x + done * ldx, ldx, 0, part + (int64_t)parts * block, n_in, 0, nullptr, 0, s);
+        if (rc) return rc;
+        ++parts;
+    }
+    const int64_t total = block;
+    reduce_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(part, parts, block, dw, n_out, n_in, lddw);
+    if (cudaGetLastError() != cudaSuccess) return cbm::fail(CBM_B200_ERR_CUDA, "dense_grad_weight: reduction launch failed");
+    return CBM_B200_OK;
+}

@@ -803,18 +803,16 @@ struct Shape {
     i32 slab_w;
     i32 n_slabs;
 };
-// Default slab width of the 128-bit path.  One slab of the operand (n_labels rows of slab_w floats)
-// is what every row gathers from while a slab is processed; it should stay resident in L2.  B200's
-// 126 MB L2 is two partitions that each keep their own copy of lines the SMs of both dies read, so
-// about half of it is usable for such an operand: 256-column slabs up to kL2SlabBytes, then
-// 128-column slabs up to the same bound, and 256 again beyond it (nothing stays resident anyway
-// and wide slabs need fewer passes over the indices).
-constexpr i64 kL2SlabBytes = 56ll << 20;
-i32 default_slab_v4(i64 n_labels) {
-    if (n_labels * 256 * 4 <= kL2SlabBytes) return 256;
-    if (n_labels * 128 * 4 <= kL2SlabBytes) return 128;
-    return 256;
-}
+// Default slab width of the 128-bit path: 128 columns, one 16-byte vector per lane.  One slab of the
+// operand (n_labels rows of slab_w floats) is what every row gathers from while that slab is
+// processed, and it should stay in L2.  B200's 126 MB L2 is two partitions that each keep their own
+// copy of lines read from both dies, so about half of it holds such an operand: at 100 000 rows a
+// 256-column slab (102 MB) does not stay, a 128-column slab (51 MB) does, and DRAM traffic halves.
+// Measured on B200, 128 columns also win where no slab can stay resident (200 000 - 400 000 rows:
+// 0.55 / 0.71 ms against 0.63 / 0.77 ms for 256 columns; 236 000 rows, width 256: 0.307 against
+// 0.324 ms): the one-vector form holds eight row fetches per lane in 56 registers and keeps 32 warps
+// per SM, the two-vector form four fetches in 72 registers and 24 warps.
+i32 default_slab_v4(i64 /*n_labels*/) { return 128; }
 
 Shape pick_shape(i32 f, i32 want_slab, bool can_v4, i64 n_labels) {
     Shape s{};
@@ -1714,7 +1712,7 @@ extern "C" double cbm_b200_probe_l2_read_gbps(int32_t device) {
     if (!g.ok) return -1.0;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const int threads = 512, blocks = sms * 4;
+    const int threads = 512, blocks = sms * 2;
     const u64 per_pass = (u64)blocks * threads * 8;            // vectors read per sweep of the grid
     const u64 n_vec = ((32ull << 20) / 16) / per_pass * per_pass;  // about 32 MB, a whole number of sweeps
     float4* buf = nullptr;

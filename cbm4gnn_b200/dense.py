@@ -1,0 +1,131 @@
+"""The dense half of a GCN layer on B200's tensor cores.
+
+A layer of the reference is ``lin`` followed by ``propagate``
+(gnns/graph_convolutional_network/cbm_gcn.py:21-24); ``lin`` is a bias-free fp32 map
+``[N, in] x [in, out]``.  ``linear(x, weight)`` runs it, and ``autograd`` its two gradients, through
+the library's fp32-accurate tensor-core GEMMs (``cbm_b200_dense_forward`` / ``_grad_input`` /
+``_grad_weight``: operands split into three bf16 terms, fp32 accumulation), which keep the 1e-4
+tolerance of the reference's tests that a single TF32 or BF16 pass would not.  CPU tensors go
+through ``torch.nn.functional.linear``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _pad4(v: int) -> int:
+    return -(-v // 4) * 4
+
+
+def _aligned(t: torch.Tensor) -> torch.Tensor:
+    """Row-major, 16-byte aligned rows (row stride a multiple of 4 floats): as is, or a copy."""
+    if t.stride(1) == 1 and t.stride(0) % 4 == 0 and t.data_ptr() % 16 == 0 and t.stride(0) >= t.size(1):
+        return t
+    out = torch.empty((t.size(0), _pad4(t.size(1))), dtype=t.dtype, device=t.device)
+    out[:, :t.size(1)].copy_(t)
+    if out.size(1) != t.size(1):
+        out[:, t.size(1):].zero_()
+    return out[:, :t.size(1)]
+
+
+def _widen(t: torch.Tensor, cols: int) -> torch.Tensor:
+    """``t`` with zero columns appended up to ``cols`` (a copy only when needed)."""
+    t = _aligned(t)
+    if t.size(1) == cols:
+        return t
+    out = torch.zeros((t.size(0), cols), dtype=t.dtype, device=t.device)
+    out[:, :t.size(1)].copy_(t)
+    return out
+
+
+def _stream(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def dense_forward(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T`` for CUDA fp32 ``x`` [N, in] and ``w`` [out, in]; ``out`` (optional) is an
+    [N, out] view with 16-byte aligned rows that receives the result."""
+    n, n_in, n_out = x.size(0), x.size(1), w.size(0)
+    ip, op = _pad4(n_in), _pad4(n_out)
+    xa, wa = _widen(x, ip), _widen(w, ip)
+    if op != n_out:
+        wp = torch.zeros((op, ip), dtype=w.dtype, device=w.device)
+        wp[:n_out].copy_(wa)
+        wa = wp
+    direct = out is not None and op == n_out and out.stride(1) == 1 and out.stride(0) % 4 == 0 and out.data_ptr() % 16 == 0
+    y = out if direct else torch.empty((n, op), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().cbm_b200_dense_forward(xa.data_ptr(), xa.stride(0), wa.data_ptr(), wa.stride(0), y.data_ptr(),
+                                                     y.stride(0), n, ip, op, _stream(x)))
+    if direct:
+        return out
+    y = y[:, :n_out]
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def dense_grad_input(gy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``gy @ w`` for ``gy`` [N, out], ``w`` [out, in]."""
+    n, n_out, n_in = gy.size(0), gy.size(1), w.size(1)
+    ip, op = _pad4(n_in), _pad4(n_out)
+    ga = _widen(gy, op)
+    wa = _widen(w, ip)
+    if op != n_out:
+        wp = torch.zeros((op, ip), dtype=w.dtype, device=w.device)
+        wp[:n_out].copy_(wa)
+        wa = wp
+    gx = torch.empty((n, ip), dtype=gy.dtype, device=gy.device)
+    with torch.cuda.device(gy.device):
+        _lib.check(_lib.lib().cbm_b200_dense_grad_input(ga.data_ptr(), ga.stride(0), wa.data_ptr(), wa.stride(0), gx.data_ptr(),
+                                                        gx.stride(0), n, ip, op, _stream(gy)))
+    return gx[:, :n_in]
+
+
+_workspaces: dict = {}
+
+
+def dense_grad_weight(gy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """``gy.T @ x`` for ``gy`` [N, out], ``x`` [N, in]: the weight gradient [out, in]."""
+    n, n_out, n_in = gy.size(0), gy.size(1), x.size(1)
+    ip, op = _pad4(n_in), _pad4(n_out)
+    ga, xa = _widen(gy, op), _widen(x, ip)
+    L = _lib.lib()
+    need = int(L.cbm_b200_dense_grad_weight_workspace(n, ip, op)) + 4 * ip * op
+    ws = _workspaces.get(gy.device)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=gy.device)
+        _workspaces[gy.device] = ws
+    gw = torch.empty((op, ip), dtype=gy.dtype, device=gy.device)
+    with torch.cuda.device(gy.device):
+        _lib.check(L.cbm_b200_dense_grad_weight(ga.data_ptr(), ga.stride(0), xa.data_ptr(), xa.stride(0), gw.data_ptr(),
+                                                gw.stride(0), n, ip, op, ws.data_ptr(), ws.numel(), _stream(gy)))
+    return gw[:n_out, :n_in]
+
+
+class _DenseMap(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return dense_forward(x, weight)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight = ctx.saved_tensors
+        gx = dense_grad_input(gy, weight) if ctx.needs_input_grad[0] else None
+        gw = dense_grad_weight(gy, x) if ctx.needs_input_grad[1] else None
+        return gx, gw
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x @ weight.T`` in fp32 accuracy, differentiable in both arguments."""
+    if not x.is_cuda:
+        return torch.nn.functional.linear(x, weight)
+    if x.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise RuntimeError("dense map: fp32 operands expected")
+    return _DenseMap.apply(x, weight)

@@ -7,26 +7,20 @@ available offline) followed by the normalized CBM propagation.  ``GCNModel`` res
 benchmark model of benchmark/parallel/benchmark_gcn_cpu.py:70-89 (ReLU between layers, one CBM
 structure shared by every layer).
 
-The dense map runs through cuBLAS in full fp32 (TF32 is switched off around it) so that results
-stay within the 1e-4 tolerance the reference's tests use.
+The dense map and its gradients run on the tensor cores through the library's fp32-accurate GEMMs
+(cbm4gnn_b200/dense.py), so that results stay within the 1e-4 tolerance the reference's tests use.
 """
 from __future__ import annotations
 
 import torch
 from torch import nn
 
+from .dense import linear
 from .message_passing import CBMCudaMessagePassing
 
 
 def _fp32_linear(lin: nn.Linear, x: torch.Tensor) -> torch.Tensor:
-    if not x.is_cuda:
-        return lin(x)
-    prev = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = False
-    try:
-        return lin(x)
-    finally:
-        torch.backends.cuda.matmul.allow_tf32 = prev
+    return linear(x, lin.weight)
 
 
 class CBMCudaGCN(CBMCudaMessagePassing):

@@ -276,12 +276,12 @@ class ShardedGCN(torch.nn.Module):
 
     @staticmethod
     def _mm(h, lin, out):
-        prev = torch.backends.cuda.matmul.allow_tf32
-        torch.backends.cuda.matmul.allow_tf32 = False  # full fp32, as the 1e-4 tolerance needs
-        try:
+        """``out = h @ lin.weight.T`` in fp32 accuracy (tensor-core GEMM on CUDA tensors)."""
+        if h.is_cuda:
+            from .dense import dense_forward
+            dense_forward(h, lin.weight, out=out)
+        else:
             torch.mm(h, lin.weight.t(), out=out)
-        finally:
-            torch.backends.cuda.matmul.allow_tf32 = prev
 
     def _gather(self, full, mine):
         import torch.distributed as dist

@@ -203,6 +203,29 @@ int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float* y, int32_
  * context stays usable. */
 int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* stream);
 
+/* --------------------------------------------------------------------------------------------
+ * Dense maps of the GCN layers: `lin` of gnns/graph_convolutional_network/cbm_gcn.py:21-24 (a
+ * bias-free [N,in] x [in,out] fp32 map, there torch_geometric's Linear on the CPU) and its two
+ * gradients, as fp32-accurate GEMMs on the tensor cores (every operand split into three bf16
+ * terms, fp32 accumulation in tensor memory).  All pointers [dev], row-major, 16-byte aligned;
+ * n_in, n_out and every leading dimension must be multiples of 4 floats.
+ *   cbm_b200_dense_forward      y [n_rows,n_out] = x [n_rows,n_in] * w^T,  w [n_out,n_in]
+ *   cbm_b200_dense_grad_input   dx [n_rows,n_in] = dy [n_rows,n_out] * w
+ *   cbm_b200_dense_grad_weight  dw [n_out,n_in]  = dy^T * x; contracts over the rows in up to
+ *                               CBM_B200_DENSE_MAX_CHUNKS independent chunks whose partial results
+ *                               are summed in a fixed order; `workspace` [dev] must hold
+ *                               cbm_b200_dense_grad_weight_workspace(...) + 4*n_in*n_out bytes.
+ * ------------------------------------------------------------------------------------------ */
+#define CBM_B200_DENSE_MAX_CHUNKS 296
+int cbm_b200_dense_forward(const float* x, int64_t ldx, const float* w, int64_t ldw, float* y,
+                           int64_t ldy, int32_t n_rows, int32_t n_in, int32_t n_out, void* stream);
+int cbm_b200_dense_grad_input(const float* dy, int64_t lddy, const float* w, int64_t ldw, float* dx,
+                              int64_t lddx, int32_t n_rows, int32_t n_in, int32_t n_out, void* stream);
+int64_t cbm_b200_dense_grad_weight_workspace(int32_t n_rows, int32_t n_in, int32_t n_out);
+int cbm_b200_dense_grad_weight(const float* dy, int64_t lddy, const float* x, int64_t ldx, float* dw,
+                               int64_t lddw, int32_t n_rows, int32_t n_in, int32_t n_out,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Measurement aid (no counterpart in the reference): GB/s at which all SMs of `device` together
  * stream a 32 MB buffer that stays resident in L2 — the ceiling of the gather traffic of the
  * product kernels.  Allocates and frees its buffer; returns a negative number on failure. */

@@ -478,12 +478,18 @@ def test_host_operands_with_ragged_width(c1):
     ei, c = c1
     n = c.num_rows
     for f in (47, 131, 5, 3):
-        x = torch.randn((n, f))
+        # integer-valued operand: the staged path cuts the width into a 128-bit part and a scalar
+        # tail, which sum in another order than the device-resident path; integers make both exact
+        x = torch.randint(-4, 5, (n, f)).float()
         want = torch.empty((n, f), device="cuda")
         c.omp_mkl_csr_spmm_update(x.cuda(), want)
         got = torch.empty((n, f))
         c.omp_mkl_csr_spmm_update(x, got)
         assert torch.equal(got, want.cpu())
+        np.testing.assert_array_equal(got.numpy(), sparse_product(ei, x.numpy(), False).astype(np.float32))
+        xr = torch.randn((n, f))
+        c.omp_mkl_csr_spmm_update(xr, got)
+        np.testing.assert_allclose(got.numpy(), sparse_product(ei, xr.numpy(), False), **TOL)
 
 
 def test_l2_probe_reports_a_plausible_rate():

@@ -51,7 +51,9 @@ def test_static_scratch_product_matches_twice_in_a_row():
         torch.testing.assert_close(got, want, atol=1e-4, rtol=1e-4)
         assert torch.equal(got, want)
         # and both against an independent float64 CSR product of the same matrix
-        ref = a64 if not normalized else a64_norm
+        # the plan carries the normalized structure (delta values +-s_col): without the row
+        # scales of the fused form it computes A D^-1/2 x
+        ref = a64_norm if normalized else a64 @ sp.diags(s)
         np.testing.assert_allclose(got.cpu().numpy(), ref @ x.cpu().numpy().astype(np.float64), atol=1e-4, rtol=1e-4)
 
 

@@ -75,6 +75,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-records of the other configurations")
+    ap.add_argument("--bare", action="store_true",
+                    help="warm-up and timed launches only (no parity sample, sustained loop, L2 probe, end-to-end, "
+                         "CPU baselines or sub-records): the command line profiler captures run")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     return ap.parse_args()
 
@@ -629,6 +632,8 @@ def main():
     rank, world, local_rank = _rank_env()
     if world != max(1, args.gpus) and world > 1:
         args.gpus = world
+    if args.bare:
+        args.no_e2e = args.no_cpu = args.no_extras = True
     from cbm4gnn_b200 import graphs
 
     if args.impl == "reference":
@@ -719,7 +724,9 @@ def main():
     plan.status(stream.cuda_stream)
 
     # parity of what was just timed: sampled owned rows against float64 CSR
-    if sh is not None:
+    if args.bare:
+        parity = dict(rows=0, max_err_over_tol=0.0, max_rel_err=0.0, max_abs_err=0.0)
+    elif sh is not None:
         full = torch.zeros((n_labels, f), device=dev)
         full[sh.begin:sh.end] = yd
         parity = shard_parity(c, sh, x, full, 1000 // world + 1, seed=rank)
@@ -734,7 +741,7 @@ def main():
 
     # sustained: back-to-back products for at least half a second, clocks sampled over the loop
     sustained = None
-    if world == 1:
+    if world == 1 and not args.bare:
         n_loop = max(args.steps, int(0.6 / max(1e-6, total_ms / args.steps * 1e-3)) + 1)
         s2 = ClockSampler(local_rank)
         s2.start()
@@ -801,7 +808,7 @@ def main():
         comp = compulsory_bytes(plan.n_rows, n_labels, plan.n_delta, f)
         comp_rate = comp / (launch_ms * 1e-3) / 1e9
         gather_bytes = 4 * f * plan.n_delta
-        l2_rate = L.cbm_b200_probe_l2_read_gbps(local_rank)
+        l2_rate = 0.0 if args.bare else L.cbm_b200_probe_l2_read_gbps(local_rank)
         roof = dict(bound="hbm", achieved=comp_rate, peak=peak, unit="GB/s", frac=comp_rate / peak, peak_source=peak_src,
                     kernel="cbm_items_kernel", launch_ms=launch_ms, compulsory_bytes_per_launch=comp,
                     what="achieved = bytes that must cross HBM at least once (X once + Y once + indices) / launch time",

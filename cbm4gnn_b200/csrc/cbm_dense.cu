@@ -87,16 +87,28 @@ int run_gemm(const char* who, int m, int n, int k, int batch, const float* a, in
                                      {m, n, k, batch},
                                      {a, sa, b, sb},
                                      {{1.0f, 0.0f}, nullptr, sd, d, sd}};
-    typename G::Gemm gemm;
-    if (gemm.can_implement(args) != cutlass::Status::kSuccess)
-        return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": shape or alignment not supported (widths and leading "
-                                                              "dimensions must be multiples of 4 floats, pointers 16-byte aligned)");
-    if (G::Gemm::get_workspace_size(args) > workspace_bytes)
-        return cbm::fail(CBM_B200_ERR_ALLOC, std::string(who) + ": workspace too small");
-    cutlass::Status st = gemm.initialize(args, workspace, stream);
-    if (st == cutlass::Status::kSuccess) st = gemm.run(stream);
-    if (st != cutlass::Status::kSuccess)
-        return cbm::fail(CBM_B200_ERR_CUDA, std::string(who) + ": " + cutlassGetStatusString(st));
+    // The TMA descriptors are encoded through the driver API, which wants a context current on the
+    // calling thread; a thread that has made no runtime call yet (an autograd worker) has none
+    // until the device is set.
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess)
+        return cbm::fail(CBM_B200_ERR_CUDA, std::string(who) + ": no usable CUDA device on this thread");
+    try {
+        typename G::Gemm gemm;
+        if (gemm.can_implement(args) != cutlass::Status::kSuccess)
+            return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": shape or alignment not supported (widths and leading "
+                                                                  "dimensions must be multiples of 4 floats, pointers 16-byte aligned)");
+        if (G::Gemm::get_workspace_size(args) > workspace_bytes)
+            return cbm::fail(CBM_B200_ERR_ALLOC, std::string(who) + ": workspace too small");
+        cutlass::Status st = gemm.initialize(args, workspace, stream);
+        if (st == cutlass::Status::kSuccess) st = gemm.run(stream);
+        if (st != cutlass::Status::kSuccess)
+            return cbm::fail(CBM_B200_ERR_CUDA, std::string(who) + ": " + cutlassGetStatusString(st));
+    } catch (const std::exception& e) {  // nothing may unwind through the C boundary
+        return cbm::fail(CBM_B200_ERR_CUDA, std::string(who) + ": " + e.what());
+    } catch (...) {
+        return cbm::fail(CBM_B200_ERR_CUDA, std::string(who) + ": unknown failure in the GEMM set-up");
+    }
     return CBM_B200_OK;
 }
 

@@ -117,6 +117,11 @@ CONFIGS = {
                x_dist="normal", seed=20243),
     "c4": dict(kind="copy", n=132_534, p_copy=0.95, n_random=20, max_degree=None, f=128, alpha=4,
                normalized=True, x_dist="uniform11", seed=20244),
+    # The fourth configuration's text estimates ~79 M stored entries (average degree ~600); with its
+    # own parameters (p = 0.95, 20 random links) the copy model produces 35 M.  "c4d" keeps the
+    # model and raises the random links to 45 per node, which yields the stated ~79 M entries.
+    "c4d": dict(kind="copy", n=132_534, p_copy=0.95, n_random=45, max_degree=None, f=128, alpha=4,
+                normalized=True, x_dist="uniform11", seed=20244),
     "c5": dict(kind="sbm", n=2_449_029, n_communities=50_000, mu=3.5, sigma=1.0, deg_in=20.0,
                deg_out=5.0, f=100, widths=(100, 256, 256, 47), alpha=2, normalized=True,
                x_dist="normal", seed=20245),

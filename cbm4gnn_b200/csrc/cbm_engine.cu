@@ -173,6 +173,14 @@ struct Vec<true> {
             : "l"(p), "r"((int)on));
         return v;
     }
+    // The same fetch without the predicate, for slabs in which every lane has columns.
+    static __device__ __forceinline__ T ld_ro(const float* p) {
+        T v;
+        asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "l"(p));
+        return v;
+    }
     static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg((const float4*)p); }
     // L2-only fetch (data written earlier in the same launch), zeros when `on` is false; volatile
     // asm for the same reason as ld_ro_if.
@@ -226,6 +234,11 @@ struct Vec<false> {
             : "l"(p), "r"((int)on));
         return v;
     }
+    static __device__ __forceinline__ T ld_ro(const float* p) {
+        T v;
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+        return v;
+    }
     static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg(p); }
     static __device__ __forceinline__ T ld_l2_if(const float* p, bool on) {
         T v;
@@ -248,7 +261,7 @@ struct Vec<false> {
 // The 32 lanes fetch 32 (col, val) pairs at once and pass them round by shuffle.  Row fetches are
 // issued UNROLL at a time so that several independent loads per lane are in flight; the weights
 // are picked up after the fetches have been issued.
-template <int NV, bool V4, int UNROLL>
+template <int NV, bool V4, int UNROLL, bool FULL = false>
 __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
                                            const float* __restrict__ val, i32 beg, i32 end,
                                            const float* __restrict__ xs, i64 ldx,
@@ -273,7 +286,10 @@ __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
                 const i32 c = __shfl_sync(0xffffffffu, mc, j + k);
                 const float* r = xs + (i64)c * ldx;
 #pragma unroll
-                for (int v = 0; v < NV; ++v) t[k][v] = V::ld_ro_if(r + v * STEP, ok[v]);
+                for (int v = 0; v < NV; ++v) {
+                    if constexpr (FULL) t[k][v] = V::ld_ro(r + v * STEP);  // every lane has columns
+                    else t[k][v] = V::ld_ro_if(r + v * STEP, ok[v]);
+                }
             }
 #pragma unroll
             for (int k = 0; k < UNROLL; ++k) {
@@ -513,6 +529,9 @@ __global__ void __launch_bounds__(256, MINB) cbm_items_kernel(const KParams p) {
                 if constexpr (V4 && NV == 1) {
                     if (wcols <= 64)
                         gather_row_half<UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0, p.ldx, wcols, acc[0], lane);
+                    else if (wcols == 128)  // a complete slab: no per-lane predicate on the fetches
+                        gather_row<NV, V4, UNROLL, true>(p.col, p.val, db.x, db.x + len, p.x + c0 + lane * V::E,
+                                                         p.ldx, ok, acc, lane);
                     else
                         gather_row<NV, V4, UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0 + lane * V::E,
                                                    p.ldx, ok, acc, lane);

@@ -96,7 +96,7 @@ def dense_grad_weight(gy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     ip, op = _pad4(n_in), _pad4(n_out)
     ga, xa = _widen(gy, op), _widen(x, ip)
     L = _lib.lib()
-    need = int(L.cbm_b200_dense_grad_weight_workspace(n, ip, op)) + 4 * ip * op
+    need = int(L.cbm_b200_dense_grad_weight_workspace(n, ip, op))
     ws = _workspaces.get(gy.device)
     if ws is None or ws.numel() < need:
         ws = torch.empty(need, dtype=torch.uint8, device=gy.device)

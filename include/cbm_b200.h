@@ -214,7 +214,7 @@ int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* stream);
  *   cbm_b200_dense_grad_weight  dw [n_out,n_in]  = dy^T * x; contracts over the rows in up to
  *                               CBM_B200_DENSE_MAX_CHUNKS independent chunks whose partial results
  *                               are summed in a fixed order; `workspace` [dev] must hold
- *                               cbm_b200_dense_grad_weight_workspace(...) + 4*n_in*n_out bytes.
+ *                               cbm_b200_dense_grad_weight_workspace(...) bytes.
  * ------------------------------------------------------------------------------------------ */
 #define CBM_B200_DENSE_MAX_CHUNKS 296
 int cbm_b200_dense_forward(const float* x, int64_t ldx, const float* w, int64_t ldw, float* y,

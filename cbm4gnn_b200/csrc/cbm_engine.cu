@@ -181,15 +181,6 @@ struct Vec<true> {
                      : "l"(p));
         return v;
     }
-    // Unpredicated fetch carrying an L2 eviction policy (createpolicy): rows of frequently named
-    // columns are kept (evict_last), the others are the first to go (evict_first).
-    static __device__ __forceinline__ T ld_ro_hint(const float* p, u64 policy) {
-        T v;
-        asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
-                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                     : "l"(p), "l"(policy));
-        return v;
-    }
     static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg((const float4*)p); }
     // L2-only fetch (data written earlier in the same launch), zeros when `on` is false; volatile
     // asm for the same reason as ld_ro_if.
@@ -248,11 +239,6 @@ struct Vec<false> {
         asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
         return v;
     }
-    static __device__ __forceinline__ T ld_ro_hint(const float* p, u64 policy) {
-        T v;
-        asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(policy));
-        return v;
-    }
     static __device__ __forceinline__ T ld_l2(const float* p) { return __ldcg(p); }
     static __device__ __forceinline__ T ld_l2_if(const float* p, bool on) {
         T v;
@@ -275,17 +261,12 @@ struct Vec<false> {
 // The 32 lanes fetch 32 (col, val) pairs at once and pass them round by shuffle.  Row fetches are
 // issued UNROLL at a time so that several independent loads per lane are in flight; the weights
 // are picked up after the fetches have been issued.
-// Column indices of a plan may carry COL_HOT in their top bit (labels are below 2^31): the column is
-// one of the most frequently named ones, whose operand rows are worth keeping in L2.
-constexpr i32 COL_HOT = (i32)0x80000000;
-constexpr i32 COL_MASK = 0x7fffffff;
-
-template <int NV, bool V4, int UNROLL, bool FULL = false, bool HINT = false>
+template <int NV, bool V4, int UNROLL, bool FULL = false>
 __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
                                            const float* __restrict__ val, i32 beg, i32 end,
                                            const float* __restrict__ xs, i64 ldx,
                                            const bool (&ok)[NV], typename Vec<V4>::T (&acc)[NV],
-                                           int lane, u64 keep = 0, u64 stream = 0) {
+                                           int lane) {
     using V = Vec<V4>;
     using T = typename V::T;
     constexpr int STEP = 32 * V::E;
@@ -302,12 +283,11 @@ __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
             T t[UNROLL][NV];
 #pragma unroll
             for (int k = 0; k < UNROLL; ++k) {
-                const i32 cm = __shfl_sync(0xffffffffu, mc, j + k);
-                const float* r = xs + (i64)(cm & COL_MASK) * ldx;
+                const i32 c = __shfl_sync(0xffffffffu, mc, j + k);
+                const float* r = xs + (i64)c * ldx;
 #pragma unroll
                 for (int v = 0; v < NV; ++v) {
-                    if constexpr (FULL && HINT) t[k][v] = V::ld_ro_hint(r + v * STEP, cm < 0 ? keep : stream);
-                    else if constexpr (FULL) t[k][v] = V::ld_ro(r + v * STEP);  // every lane has columns
+                    if constexpr (FULL) t[k][v] = V::ld_ro(r + v * STEP);  // every lane has columns
                     else t[k][v] = V::ld_ro_if(r + v * STEP, ok[v]);
                 }
             }
@@ -323,7 +303,7 @@ __device__ __forceinline__ void gather_row(const i32* __restrict__ col,
             const i32 live = n_here - j;
 #pragma unroll
             for (int k = 0; k < UNROLL; ++k) {
-                const i32 c = __shfl_sync(0xffffffffu, mc, (j + k) & 31) & COL_MASK;
+                const i32 c = __shfl_sync(0xffffffffu, mc, (j + k) & 31);
                 const float* r = xs + (i64)c * ldx;
 #pragma unroll
                 for (int v = 0; v < NV; ++v) t[k][v] = V::ld_ro_if(r + v * STEP, ok[v] && k < live);
@@ -363,7 +343,7 @@ __device__ __forceinline__ void gather_row_half(const i32* __restrict__ col,
 #pragma unroll
             for (int k = 0; k < UNROLL; ++k) {
                 const i32 idx = j + 2 * k + half;
-                const i32 c = __shfl_sync(0xffffffffu, mc, idx & 31) & COL_MASK;
+                const i32 c = __shfl_sync(0xffffffffu, mc, idx & 31);
                 t[k] = V::ld_ro_if(xs + (i64)c * ldx, okh && idx < n_here);
             }
 #pragma unroll
@@ -511,17 +491,12 @@ __device__ __forceinline__ bool finish_item(const KParams& p, i32 slab, i32 pos,
 // pointers) and the update-only mode, which gathers nothing; it is also the default form.
 // UNROLL = row fetches in flight per lane, MINB = thread blocks the register budget must allow
 // per SM.
-template <int NV, bool V4, int UNROLL, int MINB, bool HINT = false>
+template <int NV, bool V4, int UNROLL, int MINB>
 __global__ void __launch_bounds__(256, MINB) cbm_items_kernel(const KParams p) {
     using V = Vec<V4>;
     using T = typename V::T;
     constexpr int STEP = 32 * V::E;
     const int lane = threadIdx.x & 31;
-    u64 keep = 0, stream = 0;
-    if constexpr (HINT) {
-        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep));
-        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream));
-    }
     for (;;) {
         u64 t = 0;
         if (lane == 0) t = atomicAdd(p.counter, 1ULL);
@@ -555,9 +530,8 @@ __global__ void __launch_bounds__(256, MINB) cbm_items_kernel(const KParams p) {
                     if (wcols <= 64)
                         gather_row_half<UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0, p.ldx, wcols, acc[0], lane);
                     else if (wcols == 128)  // a complete slab: no per-lane predicate on the fetches
-                        gather_row<NV, V4, UNROLL, true, HINT>(p.col, p.val, db.x, db.x + len,
-                                                               p.x + c0 + lane * V::E, p.ldx, ok, acc, lane, keep,
-                                                               stream);
+                        gather_row<NV, V4, UNROLL, true>(p.col, p.val, db.x, db.x + len, p.x + c0 + lane * V::E,
+                                                         p.ldx, ok, acc, lane);
                     else
                         gather_row<NV, V4, UNROLL>(p.col, p.val, db.x, db.x + len, p.x + c0 + lane * V::E,
                                                    p.ldx, ok, acc, lane);
@@ -704,7 +678,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) cbm_items_tma_kernel(const KPar
             c = -1;
             w = 0.f;
             if (lane < NB && e < e_end) {
-                c = __ldg(p.col + e) & COL_MASK;
+                c = __ldg(p.col + e);
                 w = __ldg(p.val + e);
             }
         };
@@ -858,8 +832,6 @@ struct Shape {
 // 0.324 ms): the one-vector form holds eight row fetches per lane in 56 registers and keeps 32 warps
 // per SM, the two-vector form four fetches in 72 registers and 24 warps.
 i32 default_slab_v4(i64 /*n_labels*/) { return 128; }
-constexpr i64 kL2SlabBytes = 56ll << 20;  // a slab of the operand up to this size stays in L2 by itself
-constexpr i64 kL2HotBytes = 40ll << 20;   // slab rows of hot columns kept in L2 when it does not
 
 Shape pick_shape(i32 f, i32 want_slab, bool can_v4, i64 n_labels) {
     Shape s{};
@@ -920,8 +892,7 @@ struct cbm_b200_plan {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     std::vector<cudaEvent_t> events;
     i32 host_chunk = 0;
-    i32 form = 0;      // 0 register form, 1 bulk-copy form, 2 register form ignoring the L2 hints
-    bool hinted = false;  // col[] carries COL_HOT marks
+    i32 form = 0;      // 0 register form, 1 bulk-copy form
     float* stage_x = nullptr;
     float* stage_y = nullptr;
     i64 stage_x_cap = 0, stage_y_cap = 0;
@@ -1295,31 +1266,6 @@ int plan_from_schedule(Schedule& sch, int32_t n, int32_t n_out, bool normalized,
     p->normalized = normalized;
     cudaDeviceProp prop{};
     if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) p->sm_count = prop.multiProcessorCount;
-    // L2 residency by column frequency.  When one 128-column slab of the operand is too large to
-    // stay in L2 (see default_slab_v4), the rows of the most frequently named columns are worth
-    // keeping there and everything else is better streamed past them: mark the hottest columns, up
-    // to kL2HotBytes of slab rows, for the kernel's eviction hints.  Graphs with heavy-tailed
-    // column frequencies gain (the hottest 10 % of the columns carry 37 % of the entries of an
-    // 800 000-node copy-model graph); with flat frequencies the marks change nothing.
-    if ((i64)n_labels * 128 * 4 > kL2SlabBytes && !pcol.empty()) {
-        std::vector<i32> count((size_t)n_labels, 0);
-        for (i32 c : pcol) ++count[c];
-        const i64 budget_rows = kL2HotBytes / (128 * 4);
-        std::vector<i32> order;
-        order.reserve((size_t)n_labels);
-        for (i32 c = 0; c < n_labels; ++c)
-            if (count[c] >= 2) order.push_back(c);
-        if ((i64)order.size() > budget_rows) {
-            std::nth_element(order.begin(), order.begin() + budget_rows, order.end(),
-                             [&](i32 a, i32 b) { return count[a] != count[b] ? count[a] > count[b] : a < b; });
-            order.resize((size_t)budget_rows);
-        }
-        std::vector<char> hot((size_t)n_labels, 0);
-        for (i32 c : order) hot[c] = 1;
-        for (i32& c : pcol)
-            if (hot[c]) c |= COL_HOT;
-        p->hinted = !order.empty();
-    }
     int rc = upload(&p->d_desc, desc, p->device_bytes);
     if (rc == CBM_B200_OK) rc = upload(&p->d_col, pcol, p->device_bytes);
     if (rc == CBM_B200_OK) rc = upload(&p->d_val, pval, p->device_bytes);
@@ -1359,7 +1305,7 @@ extern "C" int cbm_b200_plan_info(const cbm_b200_plan* p, int32_t* n_rows, int64
 extern "C" int cbm_b200_plan_tune(cbm_b200_plan* p, int32_t slab_width, int32_t n_blocks,
                                   int32_t host_chunk, int32_t form) {
     if (!p) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: NULL plan");
-    if (slab_width < 0 || n_blocks < 0 || host_chunk < 0 || form < 0 || form > 2)
+    if (slab_width < 0 || n_blocks < 0 || host_chunk < 0 || form < 0 || form > 1)
         return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: knob out of range");
     if (host_chunk % 4 != 0) return cbm::fail(CBM_B200_ERR_ARG, "plan_tune: host_chunk must be a multiple of 4");
     p->form = form;
@@ -1410,7 +1356,7 @@ int plan_cfg(const cbm_b200_plan* p, const char* who, const float* x, i64 ldx, c
              i32 f, int mode, LaunchCfg& c) {
     const bool can_v4 = (f % 4 == 0) && (ldy % 4 == 0) && aligned16(y) &&
                         (mode == MODE_UPDATE_ONLY || ((ldx % 4 == 0) && aligned16(x)));
-    int tma = p->form == 1 ? 1 : 0;
+    int tma = p->form;
     if (!can_v4 || mode == MODE_UPDATE_ONLY) tma = 0;
     c.tma = tma;
     if (tma) {
@@ -1458,19 +1404,12 @@ int launch_tma(KParams& kp, int sm_count, cudaStream_t s) {
 }
 
 template <int NV, bool V4>
-int launch_regs(KParams& kp, int want_blocks, int sm_count, cudaStream_t s, bool hint = false) {
+int launch_regs(KParams& kp, int want_blocks, int sm_count, cudaStream_t s) {
     int blocks = want_blocks > 0 ? want_blocks : sm_count * 8;
     blocks = (int)std::max<i64>(1, std::min<i64>(blocks, (kp.n_claims + 7) / 8));
     kp.n_warps = (u64)blocks * 8;
     // Unroll depth and resident blocks per SM were chosen by measurement on B200: forms that
     // spill registers lose more than extra resident warps gain.
-    if constexpr (NV == 1 && V4) {
-        if (hint) {
-            cbm_items_kernel<1, true, 8, 4, true><<<blocks, 256, 0, s>>>(kp);
-            CBM_CUDA(cudaGetLastError());
-            return CBM_B200_OK;
-        }
-    }
     cbm_items_kernel<NV, V4, (NV == 1 ? 8 : 4), (NV == 1 ? 4 : (NV == 2 ? 3 : 2))><<<blocks, 256, 0, s>>>(kp);
     CBM_CUDA(cudaGetLastError());
     return CBM_B200_OK;
@@ -1518,7 +1457,7 @@ int launch_plan(cbm_b200_plan* p, const LaunchCfg& c, const float* x, i64 ldx, f
     kp.wait_ns = 2000000000ULL;
     if (c.tma) return launch_tma<256, 16, 2, 7>(kp, p->sm_count, s);
     if (c.sh.v4) {
-        if (c.sh.nv == 1) return launch_regs<1, true>(kp, p->n_blocks, p->sm_count, s, p->hinted && p->form != 2);
+        if (c.sh.nv == 1) return launch_regs<1, true>(kp, p->n_blocks, p->sm_count, s);
         if (c.sh.nv == 2) return launch_regs<2, true>(kp, p->n_blocks, p->sm_count, s);
         return launch_regs<4, true>(kp, p->n_blocks, p->sm_count, s);
     }

@@ -137,7 +137,12 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
     {
         std::vector<uint64_t> in_u(((size_t)n + 63) / 64, 0);  // bit per column: is it in row u?
                                                                 // (16 KB at n = 132 534: stays in L1)
-        std::vector<i32> hits((size_t)n, 0);   // row -> shared columns seen inside u's prefix
+        // row -> shared columns seen inside u's prefix.  The counters are hit in random order once
+        // per entry of every column list of the prefix, which is what the search spends its time
+        // on, so they are kept 16 bits wide (265 KB at n = 132 534: stays in the core's L2); the
+        // rare row whose prefix is longer than a 16-bit count can hold uses the 32-bit array.
+        std::vector<uint16_t> hits16((size_t)n, 0);
+        std::vector<i32> hits32;
         std::vector<i32> touched, cols;
 #pragma omp for schedule(dynamic, 1)
         for (i32 b = 0; b < n_blocks; ++b) {
@@ -163,18 +168,25 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
                     std::partial_sort(cols.begin(), cols.begin() + plen, cols.end(),
                                       [&](i32 x, i32 y) { return rank[x] < rank[y]; });
                 touched.clear();
-                for (i32 i = 0; i < plen; ++i) {
-                    const i32 colk = cols[i];
-                    for (i64 q = at.ptr[colk]; q < at.ptr[colk + 1]; ++q) {
-                        const i32 v = at.idx[q];
-                        if (hits[v]++ == 0) touched.push_back(v);
+                const bool wide = plen > 65000;
+                if (wide && hits32.empty()) hits32.assign((size_t)n, 0);
+                auto count_prefix = [&](auto& hits) {
+                    for (i32 i = 0; i < plen; ++i) {
+                        const i32 colk = cols[i];
+                        for (i64 q = at.ptr[colk]; q < at.ptr[colk + 1]; ++q) {
+                            const i32 v = at.idx[q];
+                            if (hits[v]++ == 0) touched.push_back(v);
+                        }
                     }
-                }
+                };
+                if (wide) count_prefix(hits32);
+                else count_prefix(hits16);
                 bool marked = false;
                 const size_t out_before = out.size();
                 for (i32 v : touched) {
-                    const i32 in_prefix = hits[v];
-                    hits[v] = 0;
+                    const i32 in_prefix = wide ? hits32[v] : (i32)hits16[v];
+                    if (wide) hits32[v] = 0;
+                    else hits16[v] = 0;
                     if (v == u || in_prefix < j_hits) continue;
                     const i32 nv = a.len(v);
                     if (nv < need) continue;

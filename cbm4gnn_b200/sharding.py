@@ -238,6 +238,8 @@ class ShardedGCN(torch.nn.Module):
       product's right-hand side), the product over the rank's subtrees;
     * "propagate_first" (in < out): an exchange of the layer input, the product at the input
       width, the dense map on the rank's own rows.
+    Wide lin_first layers (256 columns and more) are pipelined in 128-column chunks: dense map and
+    all-gather of the next chunk (side stream) run under the product of the current one.
     ReLU between layers acts on the local block.  ``exchange``: "nccl" = in-place
     ``all_gather_into_tensor``; "peer" = where the exchanged tensor is a product's output (a
     lin_first layer followed by a propagate_first layer, and the gathered model output) the
@@ -282,6 +284,20 @@ class ShardedGCN(torch.nn.Module):
             dense_forward(h, lin.weight, out=out)
         else:
             torch.mm(h, lin.weight.t(), out=out)
+
+    @staticmethod
+    def _mm_rows(h, w_rows, out):
+        """``out = h @ w_rows.T`` for a block of weight rows (a column chunk of the layer's output)."""
+        if h.is_cuda:
+            from .dense import dense_forward
+            dense_forward(h, w_rows, out=out)
+        else:
+            torch.mm(h, w_rows.t(), out=out)
+
+    def _side_stream(self, device):
+        if getattr(self, "_comm_stream", None) is None:
+            self._comm_stream = torch.cuda.Stream(device=device)
+        return self._comm_stream
 
     def _gather(self, full, mine):
         import torch.distributed as dist
@@ -339,6 +355,43 @@ class ShardedGCN(torch.nn.Module):
                     y_local.relu_()
                 t3 = tick()
                 kinds, prod = ("exchange", "product", "dense"), (h_full, p_local, ap)
+            elif sh.world > 1 and bp >= 256 and x_labels.is_cuda and not (next_gathers and self.exchange == "peer"):
+                # Wide lin_first layer: the dense map, its all-gather and the product all work on
+                # independent 128-column chunks, so chunk k+1 is mapped and gathered (on a side
+                # stream) while the product of chunk k runs.  Each chunk is its own contiguous
+                # [n_labels, 128] buffer, which the in-place all-gather needs.
+                import torch.distributed as dist
+                cur = torch.cuda.current_stream(x_labels.device)
+                comm = self._side_stream(x_labels.device)
+                cols = [(c0, min(128, bp - c0)) for c0 in range(0, bp, 128)]
+                zc, done = [], []
+                for k, (c0, w) in enumerate(cols):
+                    z = self._buffer("zc%d_%d" % (i, k), w, x_labels)
+                    zc.append(z)
+                    wr = min(w, b - c0)  # real (unpadded) columns of this chunk
+                    self._mm_rows(h_local[:, :a], lin.weight[c0:c0 + wr], z[sh.begin:sh.end, :wr])
+                    ready = torch.cuda.Event()
+                    ready.record(cur)
+                    with torch.cuda.stream(comm):
+                        comm.wait_event(ready)
+                        dist.all_gather_into_tensor(z, z[sh.begin:sh.end], group=sh.group)
+                        ev = torch.cuda.Event()
+                        ev.record(comm)
+                        done.append(ev)
+                t1 = tick()
+                cur.wait_event(done[0])
+                t2 = tick()
+                for k, (c0, w) in enumerate(cols):
+                    cur.wait_event(done[k])
+                    sh.product_into(zc[k], y_local[:, c0:c0 + w])
+                prod = (None, None, bp)
+                if timing and last:
+                    z_all = torch.cat(zc, dim=1)
+                    prod = (z_all, y_local.clone(), bp)
+                if not last:
+                    y_local.relu_()
+                t3 = tick()
+                kinds = ("dense", "exchange", "product")
             else:
                 z_full = self._buffer("z%d" % i, bp, x_labels)
                 self._mm(h_local[:, :a], lin, z_full[sh.begin:sh.end, :b])

@@ -36,8 +36,10 @@ def _worker(rank, world, port, q):
         # (100,256,47): propagate_first then lin_first; (100,64,96,47): lin_first -> propagate_first
         # -> lin_first, so with exchange="peer" one hand-over between layers and the model output
         # are delivered by the product kernel's stores into the peers' gathered buffers
+        # (100,300,256,47): its 300 -> 256 layer is lin_first and wide, so dense map, all-gather and
+        # product are pipelined over 128-column chunks
         for widths, exchange in (((100, 256, 47), "nccl"), ((100, 256, 47), "peer"), ((100, 64, 96, 47), "nccl"),
-                                 ((100, 64, 96, 47), "peer")):
+                                 ((100, 64, 96, 47), "peer"), ((100, 300, 256, 47), "nccl"), ((100, 300, 260, 47), "peer")):
             torch.manual_seed(0)
             model = ShardedGCN(widths, sh, exchange=exchange).cuda()
             h = x.astype(np.float64)

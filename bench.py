@@ -75,6 +75,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-records of the other configurations")
+    ap.add_argument("--build-gpu", action="store_true", help="--task build: candidate search on the GPU")
     ap.add_argument("--bare", action="store_true",
                     help="warm-up and timed launches only (no parity sample, sustained loop, L2 probe, end-to-end, "
                          "CPU baselines or sub-records): the command line profiler captures run")
@@ -125,7 +126,7 @@ def _rank_env():
             int(os.environ.get("LOCAL_RANK", "0")))
 
 
-def build_structure(name, scale, alpha=None, world_nodes=1, share=True):
+def build_structure(name, scale, alpha=None, world_nodes=1, share=True, build_device=None):
     """The graph of a configuration and its CBM structure.  Under torchrun rank 0 generates and
     builds with every host core and leaves the result in shared memory; the other ranks wait for it
     (N ranks building the same structure with 1/N of the cores each took N times as long)."""
@@ -153,8 +154,9 @@ def build_structure(name, scale, alpha=None, world_nodes=1, share=True):
             e = add_self_loops(e)
         t1 = time.time()
         c = cbm_matrix(e.to(torch.int32), torch.ones(e.shape[1]), alpha=cfg["alpha"], normalized=cfg["normalized"],
-                       n_threads=os.cpu_count() or 1)
+                       n_threads=os.cpu_count() or 1, build_device=build_device)
         times = dict(graph_seconds=round(t1 - t0, 2), build_seconds=round(c.build_info["seconds_total"], 3),
+                     candidates_on_gpu=c.build_info.get("candidates_on_gpu", False),
                      candidates_seconds=round(c.build_info["seconds_candidates"], 3),
                      arborescence_seconds=round(c.build_info["seconds_arborescence"], 3),
                      builder_threads=os.cpu_count() or 1)
@@ -399,15 +401,17 @@ def build_task(args):
     e32, ones = e.to(torch.int32), torch.ones(e.shape[1])
     iters = max(1, min(args.steps, 5))
     rows = []
+    build_device = 0 if (args.build_gpu and torch.cuda.is_available()) else None
     alphas = (0, 1, 2, 4, 8, 16, 32, 64) if args.alpha < 0 else (args.alpha,)
     for alpha in alphas:
         ts = []
         for _ in range(iters):
             t0 = time.perf_counter()
-            c = cbm_matrix(e32, ones, alpha=alpha, normalized=cfg["normalized"])
+            c = cbm_matrix(e32, ones, alpha=alpha, normalized=cfg["normalized"], build_device=build_device)
             ts.append(time.perf_counter() - t0)
         rows.append(dict(alpha=alpha, seconds_mean=float(np.mean(ts)), seconds_std=float(np.std(ts)),
                          native_seconds=c.build_info["seconds_total"],
+                         candidates_on_gpu=c.build_info.get("candidates_on_gpu", False),
                          candidates_seconds=c.build_info["seconds_candidates"],
                          arborescence_seconds=c.build_info["seconds_arborescence"],
                          deltas_seconds=c.build_info["seconds_deltas"], n_delta=c.build_info["n_delta"],
@@ -670,7 +674,8 @@ def main():
     from cbm4gnn_b200 import _lib
     L = _lib.lib()
     nodes = 1 if args.scaling == "strong" else world
-    c, cfg, times, shared_path = build_structure(args.workload, args.scale, args.alpha, world_nodes=nodes)
+    c, cfg, times, shared_path = build_structure(args.workload, args.scale, args.alpha, world_nodes=nodes,
+                                                 build_device=local_rank)
     f = args.f or cfg["f"]
     x = graphs.make_features(args.workload, c.num_rows, f=f)
     sh = None
@@ -853,13 +858,13 @@ def main():
     extras = {}
     if not args.no_extras and args.scale == 1.0 and args.workload == "c2":
         if world == 1:
-            c3, cfg3, t3, _ = build_structure("c3", 1.0)
+            c3, cfg3, t3, _ = build_structure("c3", 1.0, build_device=local_rank)
             x3 = graphs.make_features("c3", c3.num_rows, f=cfg3["widths"][0])
             g = gcn_fwd_bwd(c3, cfg3, x3, 10, 3, dev)
             extras["gcn_c3_fwd_bwd_ms"] = g["ms"]
             extras["gcn_c3"] = dict(g, n=c3.num_rows, n_delta=c3.build_info["n_delta"], build=t3)
             del c3, x3
-            c4, cfg4, t4, _ = build_structure("c4", 1.0)
+            c4, cfg4, t4, _ = build_structure("c4", 1.0, build_device=local_rank)
             r4 = sharded_spmm(c4, cfg4, "c4", 20, 5, dev, 0, 1)
             x4 = graphs.make_features("c4", c4.num_rows, f=cfg4["f"])
             r4["csr"] = csr_compare(c4, x4, 10, 3, dev)
@@ -867,11 +872,11 @@ def main():
             extras["c4"] = dict(r4, build=t4)
             del c4, x4
         else:
-            c4, cfg4, t4, p4 = build_structure("c4", 1.0)
+            c4, cfg4, t4, p4 = build_structure("c4", 1.0, build_device=local_rank)
             extras["c4"] = dict(sharded_spmm(c4, cfg4, "c4", 20, 5, dev, rank, world), build=t4)
             extras["c4_ms"] = extras["c4"]["ms"]
             del c4
-            c5, cfg5, t5, p5 = build_structure("c5", 1.0)
+            c5, cfg5, t5, p5 = build_structure("c5", 1.0, build_device=local_rank)
             extras["c5_gcn_forward"] = dict(sharded_gcn_forward(c5, cfg5, "c5", 5, 3, dev, rank, world), build=t5)
             extras["c5_gcn_forward_ms"] = extras["c5_gcn_forward"]["ms"]
             del c5

@@ -23,10 +23,12 @@ SOURCES = [
     os.path.join(_PKG_DIR, "csrc", "cbm_engine.cu"),
     os.path.join(_PKG_DIR, "csrc", "cbm_builder.cpp"),
     os.path.join(_PKG_DIR, "csrc", "cbm_dense.cu"),
+    os.path.join(_PKG_DIR, "csrc", "cbm_candidates.cu"),
 ]
 HEADERS = [
     os.path.join(_ROOT, "include", "cbm_b200.h"),
     os.path.join(_PKG_DIR, "csrc", "cbm_common.h"),
+    os.path.join(_PKG_DIR, "csrc", "cbm_candidates.h"),
 ]
 _OBJ_DIR = os.path.join(_PKG_DIR, "build")
 
@@ -52,6 +54,8 @@ EXPORTED = [
     "cbm_b200_last_error",
     "cbm_b200_version",
     "cbm_b200_build",
+    "cbm_b200_build_gpu",
+    "cbm_b200_built_candidates_on_gpu",
     "cbm_b200_built_info",
     "cbm_b200_built_export_csr",
     "cbm_b200_built_export_coo",
@@ -158,6 +162,9 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_version", c_char_p)
     sig("cbm_b200_build", c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int32,
         POINTER(c_void_p))
+    sig("cbm_b200_build_gpu", c_int32, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int32, c_int32,
+        POINTER(c_void_p))
+    sig("cbm_b200_built_candidates_on_gpu", c_int32, c_void_p)
     sig("cbm_b200_built_info", c_int32, c_void_p, POINTER(c_int64), POINTER(c_int64), i32p, i32p,
         POINTER(c_double))
     sig("cbm_b200_built_export_csr", c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -102,7 +102,10 @@ def _dense_args(t: torch.Tensor):
 
 class cbm_matrix:
     def __init__(self, edge_index, values, rows=None, cols=None, alpha=0, normalized=False,
-                 deltas_format="csr", n_threads=0):
+                 deltas_format="csr", n_threads=0, build_device=None):
+        """``build_device``: CUDA device ordinal on which to run the builder's candidate search
+        (the structure comes out identical; on high-degree graphs the search is nearly all of the
+        build time); None = host."""
         ei = edge_index.detach().cpu() if isinstance(edge_index, torch.Tensor) else torch.as_tensor(edge_index)
         if ei.dim() != 2 or ei.size(0) != 2:
             raise ValueError("Edge index should have shape (2, num_edges)")
@@ -125,7 +128,7 @@ class cbm_matrix:
             self.col_multiplier = deg.pow(-0.5)
             mul = _as_f32(self.col_multiplier)
 
-        self._build(row, col, n, mul, n_threads)
+        self._build(row, col, n, mul, n_threads, build_device)
         self._symmetric = None
         self._row, self._col = row, col
         self._plans: dict[int, _Plan] = {}
@@ -141,11 +144,15 @@ class cbm_matrix:
             self.deltas = csr
 
     # ------------------------------------------------------------------ construction
-    def _build(self, row, col, n, mul, n_threads):
+    def _build(self, row, col, n, mul, n_threads, build_device=None):
         L = _lib.lib()
         h = ctypes.c_void_p(0)
-        _lib.check(L.cbm_b200_build(_ptr(row), _ptr(col), row.shape[0], n, self.alpha, _ptr(mul),
-                                    int(n_threads), ctypes.byref(h)))
+        if build_device is None:
+            _lib.check(L.cbm_b200_build(_ptr(row), _ptr(col), row.shape[0], n, self.alpha, _ptr(mul),
+                                        int(n_threads), ctypes.byref(h)))
+        else:
+            _lib.check(L.cbm_b200_build_gpu(_ptr(row), _ptr(col), row.shape[0], n, self.alpha, _ptr(mul),
+                                            int(n_threads), int(build_device), ctypes.byref(h)))
         try:
             n_delta, n_cand = ctypes.c_int64(), ctypes.c_int64()
             n_rc, depth = ctypes.c_int32(), ctypes.c_int32()
@@ -161,6 +168,7 @@ class cbm_matrix:
             parent = np.empty(n, dtype=np.int32)
             _lib.check(L.cbm_b200_built_export_csr(h, _ptr(mst_row), _ptr(mst_col), _ptr(crow),
                                                    _ptr(dcol), _ptr(dval), _ptr(parent)))
+            on_gpu = L.cbm_b200_built_candidates_on_gpu(h)
         finally:
             L.cbm_b200_built_free(h)
         self.mst_row = torch.from_numpy(mst_row)
@@ -169,7 +177,7 @@ class cbm_matrix:
         self.build_info = dict(n_delta=nd, n_candidates=n_cand.value, n_root_children=n_rc.value,
                                depth=depth.value, seconds_candidates=secs[0],
                                seconds_arborescence=secs[1], seconds_deltas=secs[2],
-                               seconds_total=secs[3])
+                               seconds_total=secs[3], candidates_on_gpu=bool(on_gpu))
 
     @classmethod
     def from_arrays(cls, mst_row, mst_col, delta_crow, delta_col, delta_val, col_multiplier=None):

@@ -24,6 +24,7 @@
 #include <omp.h>
 
 #include "cbm_b200.h"
+#include "cbm_candidates.h"
 #include "cbm_common.h"
 
 namespace {
@@ -113,8 +114,11 @@ struct Candidates {
 // columns are counted through the column lists — hub columns, which make A*A^T explode, almost
 // never fall in that prefix — and only rows reaching j hits get their intersection with u counted
 // exactly.
-Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
+// device >= 0 runs the search on that GPU (cbm_candidates.cu) and falls back to the host when the
+// GPU cannot be used; the result is the same set of edges either way.  *used_gpu reports which ran.
+Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha, int device = -1, bool* used_gpu = nullptr) {
     const i32 n = a.n;
+    if (used_gpu) *used_gpu = false;
     struct Tri {
         i32 src, dst, w;
     };
@@ -127,11 +131,39 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
     });
     std::vector<i32> rank((size_t)n);
     for (i32 i = 0; i < n; ++i) rank[by_freq[i]] = i;
-    std::vector<i32>().swap(by_freq);
 
     const i32 block = 64;
     const i32 n_blocks = (n + block - 1) / block;
     std::vector<std::vector<Tri>> found((size_t)n_blocks);
+    std::vector<char> on_host;  // empty: every parent row is searched on the host
+
+    if (device >= 0 && n > 0) {
+        // rows with their columns replaced by ranks, rarest first: a prefix of such a row is the
+        // set of its rarest columns
+        std::vector<i32> row_rank(a.idx.size());
+#pragma omp parallel for schedule(dynamic, 256)
+        for (i32 r = 0; r < n; ++r) {
+            i32* b = row_rank.data() + a.ptr[r];
+            for (i64 k = a.ptr[r]; k < a.ptr[r + 1]; ++k) row_rank[(size_t)k] = rank[a.idx[(size_t)k]];
+            std::sort(b, b + a.len(r));
+        }
+        std::vector<cbm::CandTriple> triples;
+        std::vector<i32> left;
+        std::string err;
+        if (cbm::gpu_candidates(device, n, alpha, a.ptr.data(), row_rank.data(), by_freq.data(), at.ptr.data(),
+                                at.idx.data(), triples, left, err) == 0) {
+            if (used_gpu) *used_gpu = true;
+            on_host.assign((size_t)n, 0);
+            for (i32 u : left) on_host[u] = 1;
+            // in the order the host search emits: by parent block, inside a block by (parent, child)
+            std::sort(triples.begin(), triples.end(), [](const cbm::CandTriple& x, const cbm::CandTriple& y) {
+                return x.src != y.src ? x.src < y.src : x.dst < y.dst;
+            });
+            for (const cbm::CandTriple& t : triples) found[(size_t)(t.src / block)].push_back({t.src, t.dst, t.w});
+        }
+    }
+    std::vector<i32>().swap(by_freq);
+    const bool host_all = on_host.empty();
 
 #pragma omp parallel
     {
@@ -149,6 +181,7 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
             std::vector<Tri>& out = found[b];
             const i32 u_end = std::min(n, (b + 1) * block);
             for (i32 u = b * block; u < u_end; ++u) {
+                if (!host_all && !on_host[u]) continue;  // done on the GPU
                 const i32 nu = a.len(u);
                 // shared columns an edge u -> v needs: the smallest integer above (|u| + alpha) / 2,
                 // and at least one (the reference only sees pairs that intersect)
@@ -218,6 +251,12 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha) {
         }
     }
 
+    if (!host_all) {  // parents finished on the host were appended behind the GPU's: restore (parent, child) order
+#pragma omp parallel for schedule(dynamic, 16)
+        for (i32 b = 0; b < n_blocks; ++b)
+            std::sort(found[b].begin(), found[b].end(),
+                      [](const Tri& x, const Tri& y) { return x.src != y.src ? x.src < y.src : x.dst < y.dst; });
+    }
     Candidates g;
     g.off.assign((size_t)n + 1, 0);
     for (i32 v = 0; v < n; ++v) g.off[v + 1] = 1;  // virtual edge
@@ -471,11 +510,30 @@ struct cbm_b200_built {
     i32 n_root_children = 0;
     i32 depth = 0;
     double seconds[4] = {0, 0, 0, 0};
+    int candidates_on_gpu = 0;
 };
+
+namespace {
+int build_impl(const int32_t* row, const int32_t* col, int64_t nnz, int32_t n, int32_t alpha, const float* col_mul,
+               int32_t n_threads, int device, cbm_b200_built** out);
+}
 
 extern "C" int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nnz, int32_t n,
                               int32_t alpha, const float* col_mul, int32_t n_threads,
                               cbm_b200_built** out) {
+    return build_impl(row, col, nnz, n, alpha, col_mul, n_threads, -1, out);
+}
+
+extern "C" int cbm_b200_build_gpu(const int32_t* row, const int32_t* col, int64_t nnz, int32_t n,
+                                  int32_t alpha, const float* col_mul, int32_t n_threads,
+                                  int32_t device, cbm_b200_built** out) {
+    if (device < 0) return cbm::fail(CBM_B200_ERR_ARG, "build_gpu: device must be a CUDA device ordinal");
+    return build_impl(row, col, nnz, n, alpha, col_mul, n_threads, device, out);
+}
+
+namespace {
+int build_impl(const int32_t* row, const int32_t* col, int64_t nnz, int32_t n, int32_t alpha, const float* col_mul,
+               int32_t n_threads, int device, cbm_b200_built** out) {
     if (!out) return cbm::fail(CBM_B200_ERR_ARG, "build: out is NULL");
     *out = nullptr;
     if (n < 0 || nnz < 0 || (nnz > 0 && (!row || !col)))
@@ -497,7 +555,9 @@ extern "C" int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nn
         Arborescence arb;
         {
             Pattern at = transpose(a);
-            Candidates g = make_candidates(a, at, alpha);
+            bool on_gpu = false;
+            Candidates g = make_candidates(a, at, alpha, device, &on_gpu);
+            b->candidates_on_gpu = on_gpu ? 1 : 0;
             std::vector<i32>().swap(at.idx);
             b->n_candidates = g.total;
             const double t1 = now_s();
@@ -624,6 +684,9 @@ extern "C" int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nn
     if (n_threads > 0) omp_set_num_threads(prev_threads);
     return status;
 }
+}  // namespace
+
+extern "C" int cbm_b200_built_candidates_on_gpu(const cbm_b200_built* b) { return b ? b->candidates_on_gpu : 0; }
 
 extern "C" int cbm_b200_built_info(const cbm_b200_built* b, int64_t* n_delta,
                                    int64_t* n_candidates, int32_t* n_root_children,

@@ -60,6 +60,15 @@ const char* cbm_b200_version(void);
 int cbm_b200_build(const int32_t* row, const int32_t* col, int64_t nnz, int32_t n, int32_t alpha,
                    const float* col_mul, int32_t n_threads, cbm_b200_built** out);
 
+/* The same builder with its candidate search — over 95 % of the build on high-degree graphs — on
+ * CUDA device `device` (one thread block per possible parent row, hit counters in L2); arborescence
+ * and deltas stay on the host.  The candidate set, hence the structure, is identical to
+ * cbm_b200_build's.  Falls back to the host search when the GPU cannot be used (no device, out of
+ * memory); cbm_b200_built_candidates_on_gpu tells which ran (1 = GPU). */
+int cbm_b200_build_gpu(const int32_t* row, const int32_t* col, int64_t nnz, int32_t n, int32_t alpha,
+                       const float* col_mul, int32_t n_threads, int32_t device, cbm_b200_built** out);
+int cbm_b200_built_candidates_on_gpu(const cbm_b200_built* b);
+
 /* Sizes and statistics of a built structure.  Any out-pointer may be NULL.
  *   n_delta       number of delta entries (= total weight of the arborescence)
  *   n_candidates  number of candidate edges offered to the solver, virtual edges included

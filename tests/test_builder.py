@@ -237,3 +237,18 @@ def test_random_small_patterns_are_valid_and_optimal():
         assert c.build_info["n_candidates"] == len(orc.candidate_edges(ei, n, alpha))
 
     check()
+
+
+def test_gpu_build_entry_point_falls_back_to_the_host_search():
+    """Without a usable CUDA device the GPU-assisted builder runs the host search and says so; the
+    structure is the one cbm_b200_build emits."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the GPU search itself is covered by the gpu tests")
+    from cbm4gnn_b200.cbm import cbm_matrix
+    ei = torch.from_numpy(graphs.make_graph("c1", scale=0.2)).to(torch.int32)
+    a = cbm_matrix(ei, torch.ones(ei.shape[1]), alpha=2)
+    b = cbm_matrix(ei, torch.ones(ei.shape[1]), alpha=2, build_device=0)
+    assert b.build_info["candidates_on_gpu"] is False
+    assert torch.equal(a.mst_row, b.mst_row) and torch.equal(a.mst_col, b.mst_col)
+    assert np.array_equal(a._dcol, b._dcol) and np.array_equal(a._dval, b._dval)

@@ -15,6 +15,8 @@
 #include <algorithm>
 #include <chrono>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -138,6 +140,8 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha, int d
     std::vector<char> on_host;  // empty: every parent row is searched on the host
 
     if (device >= 0 && n > 0) {
+        const bool trace = std::getenv("CBM_B200_BUILD_TRACE") != nullptr;
+        const double t_a = now_s();
         // rows with their columns replaced by ranks, rarest first: a prefix of such a row is the
         // set of its rarest columns
         std::vector<i32> row_rank(a.idx.size());
@@ -150,9 +154,13 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha, int d
         std::vector<cbm::CandTriple> triples;
         std::vector<i32> left;
         std::string err;
+        const double t_b = now_s();
+        if (trace) std::fprintf(stderr, "[cbm build] rank rows %.3f s\n", t_b - t_a);
         if (cbm::gpu_candidates(device, n, alpha, a.ptr.data(), row_rank.data(), by_freq.data(), at.ptr.data(),
                                 at.idx.data(), triples, left, err) == 0) {
             if (used_gpu) *used_gpu = true;
+            if (trace) std::fprintf(stderr, "[cbm build] gpu search %.3f s, %zu edges, %zu parents left to the host\n",
+                                    now_s() - t_b, triples.size(), left.size());
             on_host.assign((size_t)n, 0);
             for (i32 u : left) on_host[u] = 1;
             // in the order the host search emits: by parent block, inside a block by (parent, child)

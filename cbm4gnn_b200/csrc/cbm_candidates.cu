@@ -15,6 +15,8 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -221,9 +223,24 @@ int gpu_candidates(int device, int32_t n, int32_t alpha, const int64_t* row_ptr,
         if ((e = cudaMalloc((void**)&p.out, (size_t)p.out_cap * sizeof(CandTriple))) != cudaSuccess) return fail("out", e);
         cudaMemset(d_count, 0, 2 * sizeof(u64));
         cudaMemset(d_n_skipped, 0, sizeof(i32));
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        const bool trace = std::getenv("CBM_B200_BUILD_TRACE") != nullptr;
+        if (trace) {
+            cudaEventCreate(&e0);
+            cudaEventCreate(&e1);
+            cudaEventRecord(e0);
+        }
         candidate_kernel<<<blocks, kThreads>>>(p);
         if ((e = cudaGetLastError()) != cudaSuccess) return fail("launch", e);
+        if (trace) cudaEventRecord(e1);
         if ((e = cudaDeviceSynchronize()) != cudaSuccess) return fail("kernel", e);
+        if (trace) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            std::fprintf(stderr, "[cbm build] candidate kernel %.3f ms\n", ms);
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+        }
         u64 h_count[2] = {0, 0};
         cudaMemcpy(h_count, d_count, sizeof(h_count), cudaMemcpyDeviceToHost);
         if ((int64_t)h_count[0] <= p.out_cap) {

@@ -164,10 +164,11 @@ Candidates make_candidates(const Pattern& a, const Pattern& at, i32 alpha, int d
             on_host.assign((size_t)n, 0);
             for (i32 u : left) on_host[u] = 1;
             // in the order the host search emits: by parent block, inside a block by (parent, child)
-            std::sort(triples.begin(), triples.end(), [](const cbm::CandTriple& x, const cbm::CandTriple& y) {
-                return x.src != y.src ? x.src < y.src : x.dst < y.dst;
-            });
             for (const cbm::CandTriple& t : triples) found[(size_t)(t.src / block)].push_back({t.src, t.dst, t.w});
+#pragma omp parallel for schedule(dynamic, 16)
+            for (i32 b = 0; b < n_blocks; ++b)
+                std::sort(found[b].begin(), found[b].end(),
+                          [](const Tri& x, const Tri& y) { return x.src != y.src ? x.src < y.src : x.dst < y.dst; });
         }
     }
     std::vector<i32>().swap(by_freq);

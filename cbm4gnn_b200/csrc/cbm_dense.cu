@@ -215,8 +215,21 @@ extern "C" int cbm_b200_dense_grad_weight(const float* dy, int64_t lddy, const f
         if (rc) return rc;
         parts = (int)chunks;
     }
-    const int64_t done = rows_per > 0 ? rows_per * chunks : 0;
-    if (done < n_rows) {  // the rows that do not fill a chunk: one more, shorter product
+    // The rows that do not fill the chunks (fewer than 16 per chunk) would be a long serial
+    // contraction for the two or four CTAs of one more product; they are cut into 64-row pieces
+    // contracted side by side, and what is left after those (< 64 rows) is one short product.
+    int64_t done = rows_per > 0 ? rows_per * chunks : 0;
+    const int64_t piece = 64;
+    const int64_t n_pieces = std::min<int64_t>((n_rows - done) / piece, CBM_B200_DENSE_MAX_CHUNKS - parts - 1);
+    if (n_pieces > 0) {
+        int rc = run_either<GemmTN, GemmTN64>(n, "dense_grad_weight", m, n, (int)piece, (int)n_pieces, a + done * lda, lda,
+                                              piece * lda, b + done * ldb, ldb, piece * ldb,
+                                              part + (int64_t)parts * block, (int64_t)n, block, (void*)nullptr, (size_t)0, s);
+        if (rc) return rc;
+        parts += (int)n_pieces;
+        done += piece * n_pieces;
+    }
+    if (done < n_rows) {
         int rc = run_either<GemmTN, GemmTN64>(n, "dense_grad_weight", m, n, (int)(n_rows - done), 1, a + done * lda, lda,
                                               (int64_t)0, b + done * ldb, ldb, (int64_t)0, part + (int64_t)parts * block,
                                               (int64_t)n, (int64_t)0, (void*)nullptr, (size_t)0, s);

@@ -80,6 +80,7 @@ EXPORTED = [
     "cbm_b200_dense_grad_weight",
     "cbm_b200_dense_grad_weight_workspace",
     "cbm_b200_spmm_update_host",
+    "cbm_b200_copy2d_async",
     "cbm_b200_spmm_update_static",
     "cbm_b200_selftest_wait",
 ]
@@ -196,6 +197,7 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_dense_grad_weight", c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32,
         c_int32, c_int32, c_void_p, c_int64, c_void_p)
     sig("cbm_b200_dense_grad_weight_workspace", c_int64, c_int32, c_int32, c_int32)
+    sig("cbm_b200_copy2d_async", c_int32, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p)
     sig("cbm_b200_spmm_update_host", c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32)
     sig("cbm_b200_spmm_update_static", c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32,
         c_int32, c_void_p)

@@ -1662,6 +1662,19 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
     return cbm_b200_plan_status(p, s);
 }
 
+// Strided copy between host and device memory on a stream: one column chunk of a row-major operand
+// (what the host-operand pipelines move).  A thin wrapper so that a host language without access to
+// the CUDA runtime's 2-D copy can drive its own pipeline (cbm4gnn_b200/sharding.py does).
+extern "C" int cbm_b200_copy2d_async(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch,
+                                     int64_t width_bytes, int64_t rows, int32_t to_device, void* stream) {
+    if (!dst || !src || width_bytes < 0 || rows < 0 || dst_pitch < width_bytes || src_pitch < width_bytes)
+        return cbm::fail(CBM_B200_ERR_ARG, "copy2d_async: bad arguments");
+    if (width_bytes == 0 || rows == 0) return CBM_B200_OK;
+    CBM_CUDA(cudaMemcpy2DAsync(dst, (size_t)dst_pitch, src, (size_t)src_pitch, (size_t)width_bytes, (size_t)rows,
+                               to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return CBM_B200_OK;
+}
+
 // ------------------------------------------------------------------------------------------
 // Self-test of the bounded wait: one warp waits, with a limit of `wait_ms`, for a ready flag that
 // nothing ever sets, and must come back with the timeout status instead of spinning forever.

@@ -180,29 +180,59 @@ class ShardedCBM:
             dist.all_gather_into_tensor(out, mine, group=self.group)
         return out
 
-    def host_product(self, x_mine_host: torch.Tensor, y_host: torch.Tensor) -> None:
+    def host_product(self, x_mine_host: torch.Tensor, y_host: torch.Tensor, chunk: int = 128) -> None:
         """The product for operands that live in host memory, one block of rows per rank.
 
-        ``x_mine_host``: this rank's block of the operand, [shard_rows, F] in label space (pinned
-        memory makes the copies asynchronous); ``y_host``: [shard_rows, F], receives this rank's
-        rows of the result.  Each rank sends only its own block over PCIe; one all-gather over
-        NVLink completes the operand on every GPU; then the product and the copy back.  Returns
-        when ``y_host`` is complete."""
+        ``x_mine_host``: this rank's block of the operand, [shard_rows, F] in label space,
+        contiguous (pinned memory makes the copies asynchronous); ``y_host``: [shard_rows, F]
+        contiguous, receives this rank's rows of the result.  Pipelined over column chunks: each rank
+        sends only its own block of a chunk over PCIe, one all-gather over NVLink completes the chunk
+        on every GPU, the product of the chunk runs and its result goes back — while the next chunk
+        is already on its way in (PCIe is full duplex).  Returns when ``y_host`` is complete."""
+        import ctypes
         import torch.distributed as dist
+        from . import _lib
+        L = _lib.lib()
+        if not (x_mine_host.is_contiguous() and y_host.is_contiguous()):
+            raise RuntimeError("host operands must be contiguous")
         f = int(x_mine_host.size(1))
+        rows = self.part.shard_rows
         dev = torch.device("cuda", self.plan.device_index)
-        bufs = self._host_bufs.get(f)
-        if bufs is None:
-            bufs = (torch.zeros((self.part.n_labels, f), device=dev), torch.zeros((self.part.shard_rows, f), device=dev))
-            self._host_bufs = {f: bufs}
-        x_full, y_dev = bufs
-        mine = x_full[self.begin:self.end]
-        mine.copy_(x_mine_host, non_blocking=True)
-        if self.world > 1:
-            dist.all_gather_into_tensor(x_full, mine, group=self.group)
-        self.product_into(x_full, y_dev)
-        y_host.copy_(y_dev, non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()
+        cols = [(c0, min(chunk, f - c0)) for c0 in range(0, f, chunk)]
+        key = (f, chunk)
+        st = self._host_bufs.get(key)
+        if st is None:
+            st = dict(xc=[torch.zeros((self.part.n_labels, w), device=dev) for _, w in cols],
+                      y=torch.zeros((rows, f), device=dev), cin=torch.cuda.Stream(dev), comm=torch.cuda.Stream(dev),
+                      cout=torch.cuda.Stream(dev))
+            self._host_bufs = {key: st}
+        cur = torch.cuda.current_stream(dev)
+        start = torch.cuda.Event()
+        start.record(cur)
+        st["cin"].wait_event(start)      # earlier work on the caller's stream (and the last call) is done
+        xp, yp = x_mine_host.data_ptr(), y_host.data_ptr()
+        for k, (c0, w) in enumerate(cols):
+            xc = st["xc"][k]
+            mine = xc[self.begin:self.end]
+            _lib.check(L.cbm_b200_copy2d_async(ctypes.c_void_p(mine.data_ptr()), w * 4, ctypes.c_void_p(xp + c0 * 4), f * 4,
+                                               w * 4, rows, 1, ctypes.c_void_p(st["cin"].cuda_stream)))
+            arrived = torch.cuda.Event()
+            arrived.record(st["cin"])
+            gathered = arrived
+            if self.world > 1:
+                with torch.cuda.stream(st["comm"]):
+                    st["comm"].wait_event(arrived)
+                    dist.all_gather_into_tensor(xc, mine, group=self.group)
+                    gathered = torch.cuda.Event()
+                    gathered.record(st["comm"])
+            cur.wait_event(gathered)
+            self.product_into(xc, st["y"][:, c0:c0 + w])
+            done = torch.cuda.Event()
+            done.record(cur)
+            st["cout"].wait_event(done)
+            _lib.check(L.cbm_b200_copy2d_async(ctypes.c_void_p(yp + c0 * 4), f * 4, ctypes.c_void_p(st["y"].data_ptr() + c0 * 4),
+                                               f * 4, w * 4, rows, 0, ctypes.c_void_p(st["cout"].cuda_stream)))
+        st["cout"].synchronize()
 
 
 class PeerBuffer:

@@ -206,6 +206,13 @@ int cbm_b200_spmm_update_bcast(cbm_b200_plan* p, const float* x, int64_t ldx, fl
 int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float* y, int32_t f,
                               int32_t normalized);
 
+/* Strided (2-D) copy of `rows` pieces of `width_bytes` between host and device memory on `stream`
+ * (to_device != 0: host -> device): one column chunk of a row-major operand.  No counterpart in the
+ * reference; lets a host-side pipeline over column chunks (multi-GPU host-operand product) be
+ * written without binding the CUDA runtime. */
+int cbm_b200_copy2d_async(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch,
+                          int64_t width_bytes, int64_t rows, int32_t to_device, void* stream);
+
 /* Self-test of the device-side bounded wait (the reference has no counterpart: its CPU walk cannot
  * stall).  One warp waits at most wait_ms (1..1000) for a flag that is never set; the call returns
  * CBM_B200_ERR_TIMEOUT when the wait gave up as designed, any other status is a failure.  The

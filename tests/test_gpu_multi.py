@@ -57,9 +57,11 @@ def _worker(rank, world, port, q):
         # operands in host memory: own block over PCIe, all-gather over NVLink, product, copy back
         xh = xl.cpu().pin_memory()
         yh = torch.empty((sh.part.shard_rows, 100)).pin_memory()
-        sh.host_product(xh[sh.begin:sh.end], yh)
         full = sh.matmul(xl)
-        assert torch.equal(yh, full[sh.begin:sh.end].cpu())
+        for chunk in (128, 32):  # one chunk, and four pipelined chunks
+            yh.fill_(float("nan"))
+            sh.host_product(xh[sh.begin:sh.end], yh, chunk=chunk)
+            torch.testing.assert_close(yh, full[sh.begin:sh.end].cpu(), atol=1e-5, rtol=1e-5)
         q.put((rank, err, err2))
     finally:
         dist.destroy_process_group()

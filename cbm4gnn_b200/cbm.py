@@ -251,38 +251,44 @@ class cbm_matrix:
 
     # ------------------------------------------------------------------ validation
     def check_format(self, edge_index):
-        """Rebuild every row's column set from the tree and the signed deltas and compare it with
-        ``edge_index``; raises ``ValueError`` on any mismatch (cbm/cbm.py:69-115)."""
+        """Validate the structure against ``edge_index``: walking the tree from the virtual root,
+        every row is its parent's column set plus the columns of its positive deltas minus those
+        of its negative deltas, and must equal the row of the matrix.  Raises ``ValueError`` with
+        the reference's messages (cbm/cbm.py:69-115) on a zero delta or any mismatch.  The matrix
+        size is the stored one; the reference derives the root index from ``edge_index[0].max()``
+        (cbm/cbm.py:71), which is wrong when the last row is empty."""
         ei = edge_index.detach().cpu().numpy() if isinstance(edge_index, torch.Tensor) else np.asarray(edge_index)
-        # the reference takes the root index from edge_index[0].max() + 1 (cbm/cbm.py:71), which
-        # is the matrix size only when the last row is non-empty; the stored size is used here
-        n_rows = self.num_rows
-        s = [set() for _ in range(n_rows + 1)]
+        n = self.num_rows
+        if np.any(self._dval == 0):
+            raise ValueError(f"Failed with the edge index: {edge_index}")
+        # the matrix as sorted unique column arrays per row
+        order = np.lexsort((ei[1], ei[0]))
+        rows_sorted, cols_sorted = ei[0][order].astype(np.int64), ei[1][order].astype(np.int64)
+        keep = np.ones(rows_sorted.shape[0], dtype=bool)
+        keep[1:] = (rows_sorted[1:] != rows_sorted[:-1]) | (cols_sorted[1:] != cols_sorted[:-1])
+        rows_sorted, cols_sorted = rows_sorted[keep], cols_sorted[keep]
+        start = np.searchsorted(rows_sorted, np.arange(n + 1))
         mr, mc = self.mst_row.numpy(), self.mst_col.numpy()
-        crow, dcol, dval = self._crow, self._dcol, self._dval
-        visited = set()
-        queue = deque([n_rows])
-        while queue:
-            u = queue.popleft()
-            if u in visited:
-                continue
-            visited.add(u)
+        crow, dcol, dval = self._crow, self._dcol.astype(np.int64), self._dval
+        rebuilt: dict[int, np.ndarray] = {n: np.empty(0, dtype=np.int64)}
+        pending = deque([n])
+        reached = 0
+        while pending:
+            u = pending.popleft()
+            base = rebuilt.pop(u)   # a row's set is only needed until its children are expanded
             for v in mc[mr[u]:mr[u + 1]].tolist():
-                queue.append(v)
-                s[v].update(s[u])
-                for c, w in zip(dcol[crow[v]:crow[v + 1]].tolist(), dval[crow[v]:crow[v + 1]].tolist()):
-                    if w > 0:
-                        s[v].add(c)
-                    elif w < 0:
-                        s[v].remove(c)
-                    else:
-                        raise ValueError(f"Failed with the edge index: {edge_index}")
-        a = [set() for _ in range(n_rows)]
-        for r, c in zip(ei[0].tolist(), ei[1].tolist()):
-            a[r].add(c)
-        for ss, sa in zip(s, a):
-            if ss != sa:
-                raise ValueError("Format is incorrect!")
+                d_cols, d_vals = dcol[crow[v]:crow[v + 1]], dval[crow[v]:crow[v + 1]]
+                minus = d_cols[d_vals < 0]
+                if minus.size and not np.all(np.isin(minus, base)):
+                    raise ValueError("Format is incorrect!")   # removes a column the parent does not have
+                row_v = np.union1d(np.setdiff1d(base, minus, assume_unique=True), d_cols[d_vals > 0])
+                if not np.array_equal(row_v, cols_sorted[start[v]:start[v + 1]]):
+                    raise ValueError("Format is incorrect!")
+                rebuilt[v] = row_v
+                pending.append(v)
+                reached += 1
+        if reached != n:
+            raise ValueError("Format is incorrect!")
 
     # ------------------------------------------------------------------ plans and dispatch
     def is_symmetric(self) -> bool:

@@ -252,3 +252,34 @@ def test_gpu_build_entry_point_falls_back_to_the_host_search():
     assert b.build_info["candidates_on_gpu"] is False
     assert torch.equal(a.mst_row, b.mst_row) and torch.equal(a.mst_col, b.mst_col)
     assert np.array_equal(a._dcol, b._dcol) and np.array_equal(a._dval, b._dval)
+
+
+def test_check_format_rejects_corrupted_structures():
+    """The validator has to fail on: a wrong matrix, a flipped delta sign, a zero delta, a column
+    removed that the parent does not hold."""
+    import torch
+    from cbm4gnn_b200.cbm import cbm_matrix
+    ei = graphs.make_graph("c1", scale=0.1)
+    e = torch.from_numpy(ei).to(torch.int32)
+    c = cbm_matrix(e, torch.ones(e.shape[1]), alpha=0)
+    c.check_format(e)
+    with pytest.raises(ValueError, match="Format is incorrect"):
+        c.check_format(e[:, :-2])                       # two entries of the matrix missing
+    keep = c._dval.copy()
+    neg = np.nonzero(c._dval < 0)[0]
+    assert neg.size > 0                                 # the graph compresses: some deltas remove columns
+    c._dval[neg[0]] = 1.0
+    with pytest.raises(ValueError, match="Format is incorrect"):
+        c.check_format(e)
+    c._dval[:] = keep
+    c._dval[0] = 0.0
+    with pytest.raises(ValueError, match="Failed with the edge index"):
+        c.check_format(e)
+    c._dval[:] = keep
+    root_child = int(c.mst_col[c.mst_row[c.num_rows]])  # a child of the virtual root removes nothing
+    k = c._crow[root_child]
+    c._dval[k] = -1.0
+    with pytest.raises(ValueError, match="Format is incorrect"):
+        c.check_format(e)
+    c._dval[:] = keep
+    c.check_format(e)

@@ -75,6 +75,8 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-records of the other configurations")
+    ap.add_argument("--contiguous", action="store_true",
+                    help="device-resident X and Y with a row pitch of exactly F floats instead of whole 128-byte lines")
     ap.add_argument("--build-gpu", action="store_true", help="--task build: candidate search on the GPU")
     ap.add_argument("--bare", action="store_true",
                     help="warm-up and timed launches only (no parity sample, sustained loop, L2 probe, end-to-end, "
@@ -692,14 +694,23 @@ def main():
         x_host = torch.from_numpy(x).pin_memory()
         n_out = n_labels = c.num_rows
     plan.tune(args.slab, args.blocks, args.host_chunk, args.form)
-    xd = x_host.to(dev, non_blocking=True)
-    yd = torch.zeros((n_out, f), device=dev)
+    # device-resident operand and result in the library's recommended layout: rows pitched to whole
+    # 128-byte lines (cbm4gnn_b200.cbm.aligned_rows); --contiguous keeps the pitch at F floats
+    from cbm4gnn_b200.cbm import aligned_rows
+    if args.contiguous:
+        xd = x_host.to(dev, non_blocking=True)
+        yd = torch.zeros((n_out, f), device=dev)
+    else:
+        xd = aligned_rows(x_host.size(0), f, dev)
+        xd.copy_(x_host, non_blocking=True)
+        yd = aligned_rows(n_out, f, dev)
+    ldx, ldy = xd.stride(0), yd.stride(0)
     y_host = torch.empty((n_out, f)).pin_memory()
     fn = L.cbm_b200_fused_spmm_update if c.normalized else L.cbm_b200_spmm_update
     stream = torch.cuda.current_stream()
 
     def step():
-        _lib.check(fn(plan.handle, xd.data_ptr(), f, yd.data_ptr(), f, f, stream.cuda_stream))
+        _lib.check(fn(plan.handle, xd.data_ptr(), ldx, yd.data_ptr(), ldy, f, stream.cuda_stream))
 
     def barrier():
         if world > 1:
@@ -838,12 +849,14 @@ def main():
                     config=workload_config(args.workload, c, cfg, f),
                     parallelism=f"root subtrees sharded over {world} GPUs, X replicated" if world > 1 else "single GPU",
                     rows_per_gpu=plan.n_rows, delta_entries_per_gpu=plan.n_delta, build=times,
+                    device_layout="row pitch %d floats (%s)" % (ldx, "contiguous" if ldx == f else "whole 128-byte lines"),
                     gpu_launches=args.steps, roofline=roof, parity=parity, clocks=clocks, sustained=sustained)
         if e2e_ms is not None:
             line["e2e"] = dict(value=ab_total / (e2e_ms_max * 1e-3) / 1e9, unit="GB/s", ms_per_step=e2e_ms_max,
                                h2d_bytes_per_step=int(sums[2].item()), d2h_bytes_per_step=int(sums[3].item()),
                                path="cbm_matrix.omp_mkl_csr_fused_spmm_update(x_cpu, y_cpu)" if world == 1 else
-                                    "ShardedCBM.host_product: own block H2D, NCCL all-gather, product, D2H")
+                                    "ShardedCBM.host_product, per 128-column chunk: own block H2D, NCCL all-gather, "
+                                    "product, D2H, chunks pipelined")
         if world == 1 and not args.no_cpu:
             per, iters, threads, kind = cpu_reference(c, x, args.cpu_seconds)
             line["cpu_baseline"] = dict(value=ab_total / per / 1e9, unit="GB/s", ms_per_step=per * 1e3, cores=threads,

@@ -1598,10 +1598,10 @@ extern "C" int cbm_b200_spmm_update_host(cbm_b200_plan* p, const float* x, float
     if (!p) return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_host: NULL plan");
     if (!x || !y || f <= 0) return cbm::fail(CBM_B200_ERR_ARG, "spmm_update_host: bad x / y / f");
     DeviceGuard g(p->device);
-    // The staging buffers use a leading dimension rounded up to 4 floats, so that rows stay
-    // 16-byte aligned whatever f is; chunks whose width is a multiple of 4 then take the 128-bit
+    // The staging buffers use a leading dimension rounded up to 32 floats, so that rows start on
+    // 128-byte lines whatever f is; chunks whose width is a multiple of 4 then take the 128-bit
     // path; a ragged last chunk is cut into a 128-bit part and a scalar tail of 1-3 columns.
-    const i64 ld = ((i64)f + 3) / 4 * 4;
+    const i64 ld = ((i64)f + 31) / 32 * 32;  // whole 128-byte lines per row: gathered pieces fill whole lines
     const i64 xb = (i64)p->n_labels * ld, yb = (i64)p->n_out * ld;
     if (xb > p->stage_x_cap) {
         cudaFree(p->stage_x);

@@ -22,7 +22,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from .cbm import _Plan, _as_f32, cbm_matrix
+from .cbm import _Plan, _as_f32, aligned_rows, cbm_matrix
 
 
 @dataclass
@@ -138,7 +138,9 @@ class ShardedCBM:
         return self._perm_t
 
     def to_labels(self, x: torch.Tensor) -> torch.Tensor:
-        out = torch.zeros((self.part.n_labels, x.size(1)), dtype=x.dtype, device=x.device)
+        """``x`` (vertex order) as a label-space operand: padding labels zero, rows pitched to whole
+        128-byte lines (see ``aligned_rows``)."""
+        out = aligned_rows(self.part.n_labels, x.size(1), x.device, x.dtype)
         out[self._perm(x.device)] = x
         return out
 
@@ -203,7 +205,7 @@ class ShardedCBM:
         st = self._host_bufs.get(key)
         if st is None:
             st = dict(xc=[torch.zeros((self.part.n_labels, w), device=dev) for _, w in cols],
-                      y=torch.zeros((rows, f), device=dev), cin=torch.cuda.Stream(dev), comm=torch.cuda.Stream(dev),
+                      y=aligned_rows(rows, f, dev), cin=torch.cuda.Stream(dev), comm=torch.cuda.Stream(dev),
                       cout=torch.cuda.Stream(dev))
             self._host_bufs = {key: st}
         cur = torch.cuda.current_stream(dev)
@@ -231,7 +233,7 @@ class ShardedCBM:
             done.record(cur)
             st["cout"].wait_event(done)
             _lib.check(L.cbm_b200_copy2d_async(ctypes.c_void_p(yp + c0 * 4), f * 4, ctypes.c_void_p(st["y"].data_ptr() + c0 * 4),
-                                               f * 4, w * 4, rows, 0, ctypes.c_void_p(st["cout"].cuda_stream)))
+                                               st["y"].stride(0) * 4, w * 4, rows, 0, ctypes.c_void_p(st["cout"].cuda_stream)))
         st["cout"].synchronize()
 
 

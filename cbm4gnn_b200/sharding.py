@@ -270,8 +270,10 @@ class ShardedGCN(torch.nn.Module):
       product's right-hand side), the product over the rank's subtrees;
     * "propagate_first" (in < out): an exchange of the layer input, the product at the input
       width, the dense map on the rank's own rows.
-    Wide lin_first layers (256 columns and more) are pipelined in 128-column chunks: dense map and
-    all-gather of the next chunk (side stream) run under the product of the current one.
+    ``pipeline_wide``: lin_first layers of 256 columns and more run in 128-column chunks, dense map
+    and all-gather of the next chunk (side stream) under the product of the current one.  Measured on
+    the 2.4 M-node block-model graph the 256-wide layer goes from 8.8 to 8.2 ms on 2 GPUs but from
+    5.05 to 5.36 ms on 8 (the all-gather and the product slow each other down), so it is off by default.
     ReLU between layers acts on the local block.  ``exchange``: "nccl" = in-place
     ``all_gather_into_tensor``; "peer" = where the exchanged tensor is a product's output (a
     lin_first layer followed by a propagate_first layer, and the gathered model output) the
@@ -280,11 +282,12 @@ class ShardedGCN(torch.nn.Module):
     Everything lives in label space; padding rows are zero and stay zero (no bias).
     """
 
-    def __init__(self, widths, sharded: ShardedCBM, exchange: str = "nccl"):
+    def __init__(self, widths, sharded: ShardedCBM, exchange: str = "nccl", pipeline_wide: bool = False):
         super().__init__()
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
         self.sharded = sharded
+        self.pipeline_wide = pipeline_wide
         self.exchange = exchange if sharded.world > 1 else "nccl"
         self._cache = {}
         self._peer = {}
@@ -387,7 +390,8 @@ class ShardedGCN(torch.nn.Module):
                     y_local.relu_()
                 t3 = tick()
                 kinds, prod = ("exchange", "product", "dense"), (h_full, p_local, ap)
-            elif sh.world > 1 and bp >= 256 and x_labels.is_cuda and not (next_gathers and self.exchange == "peer"):
+            elif (self.pipeline_wide and sh.world > 1 and bp >= 256 and x_labels.is_cuda
+                  and not (next_gathers and self.exchange == "peer")):
                 # Wide lin_first layer: the dense map, its all-gather and the product all work on
                 # independent 128-column chunks, so chunk k+1 is mapped and gathered (on a side
                 # stream) while the product of chunk k runs.  Each chunk is its own contiguous

@@ -41,7 +41,7 @@ def _worker(rank, world, port, q):
         for widths, exchange in (((100, 256, 47), "nccl"), ((100, 256, 47), "peer"), ((100, 64, 96, 47), "nccl"),
                                  ((100, 64, 96, 47), "peer"), ((100, 300, 256, 47), "nccl"), ((100, 300, 260, 47), "peer")):
             torch.manual_seed(0)
-            model = ShardedGCN(widths, sh, exchange=exchange).cuda()
+            model = ShardedGCN(widths, sh, exchange=exchange, pipeline_wide=len(widths) == 4).cuda()
             h = x.astype(np.float64)
             for k, l in enumerate(model.lins):
                 w = l.weight.detach().cpu().numpy().astype(np.float64)

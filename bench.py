@@ -833,6 +833,9 @@ def main():
                                 l2_to_sm_peak=l2_rate, frac=(gather_bytes / (launch_ms * 1e-3) / 1e9) / l2_rate if l2_rate > 0 else None,
                                 unit="GB/s", what="operand rows gathered per launch against the rate at which all SMs "
                                                   "stream an L2-resident buffer (measured in this run)"))
+        # which resource actually bounds the kernel, said in so many words for the reader of the line
+        roof["binding_resource"] = "l2_to_sm (operand rows are gathered out of L2; HBM carries only the compulsory bytes)"
+        roof["frac_of_binding_resource"] = roof["gather"]["frac"]
         cap, why = recorded_traffic(args.workload, f, world, args.scale, cfg["alpha"])
         if cap is not None:
             roof["traffic"] = cap["dram_bytes_per_launch"]

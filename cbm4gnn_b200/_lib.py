@@ -108,7 +108,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB_PATH
     os.makedirs(_OBJ_DIR, exist_ok=True)
     newest_header = max(os.path.getmtime(h) for h in HEADERS)
-    objs, log = [], []
+    objs, jobs = [], []
     for src in SOURCES:
         obj = os.path.join(_OBJ_DIR, os.path.splitext(os.path.basename(src))[0] + ".o")
         objs.append(obj)
@@ -128,10 +128,18 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
         cmd += ["-c", src, "-o", obj]
+        jobs.append(cmd)
+
+    def compile_one(cmd):
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
-        log.append(res.stderr)
+        return res.stderr
+
+    # the sources are compiled side by side: the CUTLASS instantiations alone take minutes
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=max(1, len(jobs))) as pool:
+        log = list(pool.map(compile_one, jobs))
     cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB_PATH, *objs, "-lgomp"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:

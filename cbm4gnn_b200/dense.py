@@ -91,7 +91,9 @@ _workspaces: dict = {}
 
 
 def dense_grad_weight(gy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
-    """``gy.T @ x`` for ``gy`` [N, out], ``x`` [N, in]: the weight gradient [out, in]."""
+    """``gy.T @ x`` for ``gy`` [N, out], ``x`` [N, in]: the weight gradient [out, in].  The partial
+    results of the row chunks go through one workspace per device, so calls on one device must not
+    overlap (autograd issues them on one stream)."""
     n, n_out, n_in = gy.size(0), gy.size(1), x.size(1)
     ip, op = _pad4(n_in), _pad4(n_out)
     ga, xa = _widen(gy, op), _widen(x, ip)

@@ -23,12 +23,14 @@ SOURCES = [
     os.path.join(_PKG_DIR, "csrc", "cbm_engine.cu"),
     os.path.join(_PKG_DIR, "csrc", "cbm_builder.cpp"),
     os.path.join(_PKG_DIR, "csrc", "cbm_dense.cu"),
+    os.path.join(_PKG_DIR, "csrc", "cbm_dense_grad.cu"),
     os.path.join(_PKG_DIR, "csrc", "cbm_candidates.cu"),
 ]
 HEADERS = [
     os.path.join(_ROOT, "include", "cbm_b200.h"),
     os.path.join(_PKG_DIR, "csrc", "cbm_common.h"),
     os.path.join(_PKG_DIR, "csrc", "cbm_candidates.h"),
+    os.path.join(_PKG_DIR, "csrc", "cbm_dense_gemm.cuh"),
 ]
 _OBJ_DIR = os.path.join(_PKG_DIR, "build")
 
@@ -76,6 +78,7 @@ EXPORTED = [
     "cbm_b200_spmm_update_bcast",
     "cbm_b200_probe_l2_read_gbps",
     "cbm_b200_dense_forward",
+    "cbm_b200_dense_forward_relu",
     "cbm_b200_dense_grad_input",
     "cbm_b200_dense_grad_weight",
     "cbm_b200_dense_grad_weight_workspace",
@@ -121,7 +124,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             "-I", os.path.join(_ROOT, "include"),
             "-I", os.path.join(_PKG_DIR, "csrc"),
         ]
-        if src.endswith("cbm_dense.cu"):
+        if os.path.basename(src).startswith("cbm_dense"):
             cmd += ["--expt-relaxed-constexpr", "-diag-suppress", "20012"]
             for inc in _cutlass_includes():
                 cmd += ["-I", inc]
@@ -200,7 +203,7 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_spmm_update_bcast", c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32,
         c_int32, c_int32, POINTER(c_void_p), c_void_p)
     sig("cbm_b200_probe_l2_read_gbps", c_double, c_int32)
-    for name in ("cbm_b200_dense_forward", "cbm_b200_dense_grad_input"):
+    for name in ("cbm_b200_dense_forward", "cbm_b200_dense_forward_relu", "cbm_b200_dense_grad_input"):
         sig(name, c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p)
     sig("cbm_b200_dense_grad_weight", c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32,
         c_int32, c_int32, c_void_p, c_int64, c_void_p)

@@ -46,9 +46,10 @@ def _stream(t: torch.Tensor) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
-def dense_forward(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``x @ w.T`` for CUDA fp32 ``x`` [N, in] and ``w`` [out, in]; ``out`` (optional) is an
-    [N, out] view with 16-byte aligned rows that receives the result."""
+def dense_forward(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, relu: bool = False) -> torch.Tensor:
+    """``x @ w.T`` (``relu``: followed by ``max(., 0)`` in the GEMM's epilogue) for CUDA fp32 ``x``
+    [N, in] and ``w`` [out, in]; ``out`` (optional) is an [N, out] view with 16-byte aligned rows
+    that receives the result."""
     n, n_in, n_out = x.size(0), x.size(1), w.size(0)
     ip, op = _pad4(n_in), _pad4(n_out)
     xa, wa = _widen(x, ip), _widen(w, ip)
@@ -59,8 +60,8 @@ def dense_forward(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = N
     direct = out is not None and op == n_out and out.stride(1) == 1 and out.stride(0) % 4 == 0 and out.data_ptr() % 16 == 0
     y = out if direct else torch.empty((n, op), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(_lib.lib().cbm_b200_dense_forward(xa.data_ptr(), xa.stride(0), wa.data_ptr(), wa.stride(0), y.data_ptr(),
-                                                     y.stride(0), n, ip, op, _stream(x)))
+        fn = _lib.lib().cbm_b200_dense_forward_relu if relu else _lib.lib().cbm_b200_dense_forward
+        _lib.check(fn(xa.data_ptr(), xa.stride(0), wa.data_ptr(), wa.stride(0), y.data_ptr(), y.stride(0), n, ip, op, _stream(x)))
     if direct:
         return out
     y = y[:, :n_out]
@@ -122,6 +123,33 @@ class _DenseMap(torch.autograd.Function):
         gx = dense_grad_input(gy, weight) if ctx.needs_input_grad[0] else None
         gw = dense_grad_weight(gy, x) if ctx.needs_input_grad[1] else None
         return gx, gw
+
+
+class _DenseMapRelu(torch.autograd.Function):
+    """``relu(x @ w.T)`` with the ReLU in the GEMM's epilogue; the gradient masks with the output."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        h = dense_forward(x, weight, relu=True)
+        ctx.save_for_backward(x, weight, h)
+        return h
+
+    @staticmethod
+    def backward(ctx, gh):
+        x, weight, h = ctx.saved_tensors
+        gy = gh * (h > 0)
+        gx = dense_grad_input(gy, weight) if ctx.needs_input_grad[0] else None
+        gw = dense_grad_weight(gy, x) if ctx.needs_input_grad[1] else None
+        return gx, gw
+
+
+def linear_relu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``relu(x @ weight.T)`` in fp32 accuracy, differentiable in both arguments."""
+    if not x.is_cuda:
+        return torch.nn.functional.linear(x, weight).relu()
+    if x.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise RuntimeError("dense map: fp32 operands expected")
+    return _DenseMapRelu.apply(x, weight)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

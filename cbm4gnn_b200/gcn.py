@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .dense import linear
+from .dense import linear, linear_relu
 from .message_passing import CBMCudaMessagePassing
 
 
@@ -48,11 +48,15 @@ class CBMCudaGCN(CBMCudaMessagePassing):
     def product_width(self) -> int:
         return self.in_channels if self.propagate_first() else self.out_channels
 
-    def forward(self, x, edge_index):
+    def forward(self, x, edge_index, relu: bool = False):
+        """``relu``: apply the ReLU that follows this layer in a stack; when the dense map comes
+        last in the layer it runs in the map's epilogue."""
         if self.propagate_first():
-            return _fp32_linear(self.lin, super().forward(edge_index, x=x))
+            p = super().forward(edge_index, x=x)
+            return linear_relu(p, self.lin.weight) if relu else _fp32_linear(self.lin, p)
         x = _fp32_linear(self.lin, x)
-        return super().forward(edge_index, x=x)
+        y = super().forward(edge_index, x=x)
+        return y.relu() if relu else y
 
 
 # Reference class names (cbm_gcn.py:10, 27, 44, 61).
@@ -92,8 +96,7 @@ class GCNModel(nn.Module):
             layer.cached_a_t = structure
 
     def forward(self, x, edge_index):
+        last = len(self.layers) - 1
         for i, layer in enumerate(self.layers):
-            if i:
-                x = x.relu()
-            x = layer(x, edge_index)
+            x = layer(x, edge_index, relu=i < last)
         return x

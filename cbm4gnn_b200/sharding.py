@@ -312,13 +312,16 @@ class ShardedGCN(torch.nn.Module):
         return self._peer[key]
 
     @staticmethod
-    def _mm(h, lin, out):
-        """``out = h @ lin.weight.T`` in fp32 accuracy (tensor-core GEMM on CUDA tensors)."""
+    def _mm(h, lin, out, relu=False):
+        """``out = h @ lin.weight.T`` (``relu``: then ``max(., 0)``) in fp32 accuracy (tensor-core
+        GEMM on CUDA tensors, the ReLU in its epilogue)."""
         if h.is_cuda:
             from .dense import dense_forward
-            dense_forward(h, lin.weight, out=out)
+            dense_forward(h, lin.weight, out=out, relu=relu)
         else:
             torch.mm(h, lin.weight.t(), out=out)
+            if relu:
+                out.relu_()
 
     @staticmethod
     def _mm_rows(h, w_rows, out):
@@ -385,9 +388,7 @@ class ShardedGCN(torch.nn.Module):
                 p_local = self._buffer("p%d" % i, ap, x_labels, rows=sh.part.shard_rows)
                 sh.product_into(h_full, p_local)
                 t2 = tick()
-                self._mm(p_local[:, :a], lin, y_local[:, :b])
-                if not last:
-                    y_local.relu_()
+                self._mm(p_local[:, :a], lin, y_local[:, :b], relu=not last)
                 t3 = tick()
                 kinds, prod = ("exchange", "product", "dense"), (h_full, p_local, ap)
             elif (self.pipeline_wide and sh.world > 1 and bp >= 256 and x_labels.is_cuda

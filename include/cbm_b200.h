@@ -226,6 +226,8 @@ int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* stream);
  * terms, fp32 accumulation in tensor memory).  All pointers [dev], row-major, 16-byte aligned;
  * n_in, n_out and every leading dimension must be multiples of 4 floats.
  *   cbm_b200_dense_forward      y [n_rows,n_out] = x [n_rows,n_in] * w^T,  w [n_out,n_in]
+ *   cbm_b200_dense_forward_relu y = max(x * w^T, 0): the map followed by the ReLU that sits between two
+ *                               layers (benchmark/parallel/benchmark_gcn_cpu.py:70-89), in the epilogue
  *   cbm_b200_dense_grad_input   dx [n_rows,n_in] = dy [n_rows,n_out] * w
  *   cbm_b200_dense_grad_weight  dw [n_out,n_in]  = dy^T * x; contracts over the rows in up to
  *                               CBM_B200_DENSE_MAX_CHUNKS independent chunks whose partial results
@@ -235,6 +237,8 @@ int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* stream);
 #define CBM_B200_DENSE_MAX_CHUNKS 296
 int cbm_b200_dense_forward(const float* x, int64_t ldx, const float* w, int64_t ldw, float* y,
                            int64_t ldy, int32_t n_rows, int32_t n_in, int32_t n_out, void* stream);
+int cbm_b200_dense_forward_relu(const float* x, int64_t ldx, const float* w, int64_t ldw, float* y,
+                                int64_t ldy, int32_t n_rows, int32_t n_in, int32_t n_out, void* stream);
 int cbm_b200_dense_grad_input(const float* dy, int64_t lddy, const float* w, int64_t ldw, float* dx,
                               int64_t lddx, int32_t n_rows, int32_t n_in, int32_t n_out, void* stream);
 int64_t cbm_b200_dense_grad_weight_workspace(int32_t n_rows, int32_t n_in, int32_t n_out);

@@ -47,3 +47,25 @@ def test_autograd_and_strided_operands():
     dense.dense_forward(x.detach(), w.detach(), out=out[:, 4:68])
     _check(out[:, 4:68], yr.detach())
     assert (out[:, :4] == -1).all() and (out[:, 68:] == -1).all()
+
+
+def test_relu_in_the_epilogue():
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn((30_000, 128), device="cuda", generator=g).requires_grad_(True)
+    w = (torch.randn((256, 128), device="cuda", generator=g) * 0.1).requires_grad_(True)
+    h = dense.linear_relu(x, w)
+    gy = torch.randn(h.shape, device="cuda", generator=g)
+    h.backward(gy)
+    xr, wr = x.detach().double().requires_grad_(True), w.detach().double().requires_grad_(True)
+    pre = xr @ wr.t()
+    # same mask as the fp32 result: pre-activations within rounding of zero may differ in sign
+    mask = (h.detach() > 0)
+    assert ((mask != (pre.detach() > 0)) & (pre.detach().abs() > 1e-5)).sum().item() == 0
+    hr = pre * mask
+    hr.backward(gy.double())
+    _check(h.detach(), hr.detach())
+    _check(x.grad, xr.grad)
+    _check(w.grad, wr.grad)
+    out = torch.empty((30_000, 47), device="cuda")
+    dense.dense_forward(x.detach(), w.detach()[:47], out=out, relu=True)     # ragged width, narrow tiles
+    _check(out, (x.detach().double() @ w.detach()[:47].double().t()).clamp_min(0))

@@ -137,7 +137,7 @@ class _DenseMapRelu(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gh):
         x, weight, h = ctx.saved_tensors
-        gy = gh * (h > 0)
+        gy = torch.ops.aten.threshold_backward(gh, h, 0.0)  # gh where h > 0, else 0: one pass
         gx = dense_grad_input(gy, weight) if ctx.needs_input_grad[0] else None
         gw = dense_grad_weight(gy, x) if ctx.needs_input_grad[1] else None
         return gx, gw

@@ -602,6 +602,9 @@ def sharded_spmm(c, cfg, name, steps, warmup, dev, rank, world):
     ms = e0.elapsed_time(e1) / steps
     par = shard_parity(c, sh, x, out, 1000 // world + 1, seed=rank)
     ab = algorithmic_bytes(sh.plan.n_rows, sh.plan.n_delta, sh.plan.n_root_children, f)
+    exchange = None
+    if world > 1:
+        exchange = product_with_exchange(sh, xl, out, f, steps, dev)
     stats = torch.tensor([ms, par["max_err_over_tol"], par["max_rel_err"]], dtype=torch.float64, device=dev)
     tot = torch.tensor([float(ab), float(par["rows"])], dtype=torch.float64, device=dev)
     if world > 1:
@@ -609,8 +612,61 @@ def sharded_spmm(c, cfg, name, steps, warmup, dev, rank, world):
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
     return dict(workload=name, n=c.num_rows, n_delta=c.build_info["n_delta"], f=f, alpha=cfg["alpha"], n_gpus=world,
                 ms=stats[0].item(), steps=steps, scaling="strong", algorithmic_GBps=tot[0].item() / (stats[0].item() * 1e-3) / 1e9,
+                product_plus_exchange=exchange,
                 parity=dict(rows=int(tot[1].item()), against="float64 csr", max_err_over_tol=stats[1].item(),
                             max_rel_err=stats[2].item()))
+
+
+def product_with_exchange(sh, xl, out, f, steps, dev):
+    """The product followed by the exchange that hands its result to every GPU (what a layer output
+    needs), two ways: the product, then an NCCL all-gather of the shards; and the product kernel
+    delivering every finished row itself into all GPUs' gathered buffers (ordinary peer stores over
+    NVLink while the product runs) followed by one barrier.  Times are the maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+    res = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def nccl():
+        mine = sh.local_product(xl, out)
+        dist.all_gather_into_tensor(out, mine, group=sh.group)
+
+    res["nccl_ms"] = timed(nccl)
+    want = out.clone()
+    try:
+        from cbm4gnn_b200.sharding import PeerBuffer
+        pb = PeerBuffer(sh.part.n_labels, f, dev, sh.group)
+        raw = torch.zeros((sh.part.shard_rows, f), device=dev)
+        dst = pb.slice_addresses(sh.begin)
+
+        def fused():
+            pb.barrier()
+            sh.product_into(xl, raw, bcast=dst)
+            pb.barrier()
+
+        res["fused_peer_store_ms"] = timed(fused)
+        same = torch.tensor([1.0 if torch.equal(pb.tensor, want) else 0.0], dtype=torch.float64, device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        res["fused_equals_nccl"] = bool(same.item() == 1.0)
+    except Exception as e:  # symmetric memory not available on this box: the NCCL figure stands alone
+        res["fused_peer_store_ms"] = None
+        res["note"] = "peer-store delivery not measured: " + str(e).splitlines()[0][:200]
+    return res
 
 
 def shard_parity(c, sh, x, out_labels, n_rows, seed=0):

@@ -43,7 +43,8 @@ def search_alpha(edge_index, f: int, alphas=DEFAULT_ALPHAS, normalized: bool = F
     table = []
     x = y = None
     for alpha in alphas:
-        c = cbm_matrix(ei.to(torch.int32), values, alpha=int(alpha), normalized=normalized)
+        c = cbm_matrix(ei.to(torch.int32), values, alpha=int(alpha), normalized=normalized,
+                       build_device=torch.cuda.current_device() if measure else None)
         info = c.build_info
         row = dict(alpha=int(alpha), n_delta=info["n_delta"], n_root_children=info["n_root_children"],
                    depth=info["depth"], compression_ratio=c.compression_ratio(),

@@ -33,12 +33,17 @@ class CBMCudaMessagePassing(nn.Module):
 
     two_step = False  # True: delta product, then the update-only kernel
 
-    def _structure(self, edge_index: torch.Tensor, dtype) -> cbm_matrix:
+    def _structure(self, edge_index: torch.Tensor, dtype, device=None) -> cbm_matrix:
         if self.cached and self.cached_a_t is not None:
             return self.cached_a_t
         edge_index_t = torch.stack([edge_index[1], edge_index[0]], dim=0).to(torch.int32)
+        # the builder's candidate search runs on the GPU that holds the features (same structure,
+        # several times faster on high-degree graphs)
+        build_device = device.index if device is not None and device.type == "cuda" else None
+        if build_device is None and device is not None and device.type == "cuda":
+            build_device = torch.cuda.current_device()
         a_t = cbm_matrix(edge_index_t, torch.ones(edge_index.size(1), dtype=dtype),
-                         normalized=self.normalize, alpha=self.alpha)
+                         normalized=self.normalize, alpha=self.alpha, build_device=build_device)
         if self.cached:
             self.cached_a_t = a_t
         return a_t
@@ -47,7 +52,7 @@ class CBMCudaMessagePassing(nn.Module):
         if "x" not in kwargs:
             raise ValueError("x must be in kwargs")
         x = kwargs["x"]
-        return self._structure(edge_index, x.dtype).matmul(x, two_step=self.two_step)
+        return self._structure(edge_index, x.dtype, x.device).matmul(x, two_step=self.two_step)
 
 
 # Reference class names (cbm_message_passing.py:7, 39, 63, 90).

@@ -1405,12 +1405,17 @@ int launch_tma(KParams& kp, int sm_count, cudaStream_t s) {
 
 template <int NV, bool V4>
 int launch_regs(KParams& kp, int want_blocks, int sm_count, cudaStream_t s) {
-    int blocks = want_blocks > 0 ? want_blocks : sm_count * 8;
+    // Unroll depth and resident blocks per SM were chosen by measurement on B200.  For the default
+    // form (one float4 per lane, 128-column slabs) 4 gathers in flight per warp at 48 resident
+    // warps per SM (40 registers) beat 8 in flight at 32 warps (64 registers) by 3 % on wide
+    // operands and tie on narrow ones; forms that spill registers lose more than extra resident
+    // warps gain.
+    constexpr int kUnroll = NV == 1 ? (V4 ? 4 : 8) : 4;
+    constexpr int kResident = NV == 1 ? (V4 ? 6 : 4) : (NV == 2 ? 3 : 2);
+    int blocks = want_blocks > 0 ? want_blocks : sm_count * (NV == 1 && V4 ? kResident : 8);
     blocks = (int)std::max<i64>(1, std::min<i64>(blocks, (kp.n_claims + 7) / 8));
     kp.n_warps = (u64)blocks * 8;
-    // Unroll depth and resident blocks per SM were chosen by measurement on B200: forms that
-    // spill registers lose more than extra resident warps gain.
-    cbm_items_kernel<NV, V4, (NV == 1 ? 8 : 4), (NV == 1 ? 4 : (NV == 2 ? 3 : 2))><<<blocks, 256, 0, s>>>(kp);
+    cbm_items_kernel<NV, V4, kUnroll, kResident><<<blocks, 256, 0, s>>>(kp);
     CBM_CUDA(cudaGetLastError());
     return CBM_B200_OK;
 }

@@ -30,6 +30,28 @@ using ColMajor = cutlass::layout::ColumnMajor;
 // shared memory.  Measured on B200 (N = 235 868 rows): 128 x 128 x 16 tiles 0.20 ms for 128 -> 256 and
 // 0.18 ms for 256 -> 128 (cuBLAS fp32 SIMT: 0.33 / 0.31 ms); a 64-column result takes 0.10 ms with
 // 128 x 64 tiles against 0.18 ms with 128 x 128 tiles (half of every tile wasted).
+// The collective builder fixes the number of computed bands (anti-diagonals i + j of the products
+// a_i b_j of the three-term splits) at 5 = all 9 products.  Rebuilds its result with another count.
+template <class Op, int Bands>
+struct WithBands;
+template <int L2T, int T2M, int Sch, int Acc, int NB, int SF, int API, class CS, class ACA, class Arch, class... Rest,
+          int Bands>
+struct WithBands<cutlass::gemm::collective::CollectiveMma<
+                     cutlass::gemm::MainloopSm100TmaUmmaWarpSpecializedFastF32<L2T, T2M, Sch, Acc, NB, SF, API, CS, ACA, Arch>,
+                     Rest...>,
+                 Bands> {
+    using type = cutlass::gemm::collective::CollectiveMma<
+        cutlass::gemm::MainloopSm100TmaUmmaWarpSpecializedFastF32<L2T, T2M, Sch, Acc, Bands, SF, API, CS, ACA, Arch>, Rest...>;
+};
+
+// Three bands = the six products a_i b_j with i + j <= 2.  The three dropped ones are below 2^-24 of
+// |a||b|; measured against float64 the result errs by 1.2e-7 of sum |a||b| (cuBLAS fp32: 4e-7), and a
+// training step of the 2-layer GCN takes 1.58 ms instead of 1.61 ms with all nine.  128 x 128 x 32
+// tiles (3 + 3 pipeline stages instead of 7 + 6) were measured 4 % slower than 128 x 128 x 16.
+#ifndef CBM_DENSE_BANDS
+#define CBM_DENSE_BANDS 3
+#endif
+
 template <class LayoutA, class LayoutB, int TileN, int TileK, bool Relu = false>
 struct FastGemm {
     using TileShape = Shape<_128, Int<TileN>, Int<TileK>>;
@@ -42,11 +64,12 @@ struct FastGemm {
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, TileShape, ClusterShape,
         cutlass::epilogue::collective::EpilogueTileAuto, float, float, float, RowMajor, 4, float, RowMajor, 4,
         cutlass::epilogue::TmaWarpSpecialized1Sm, Fusion>::CollectiveOp;
-    using CollectiveMainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+    using BuiltMainloop = typename cutlass::gemm::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, float, TileShape,
         ClusterShape,
         cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename CollectiveEpilogue::SharedStorage))>,
         cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>::CollectiveOp;
+    using CollectiveMainloop = typename WithBands<BuiltMainloop, CBM_DENSE_BANDS>::type;
     using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, CollectiveMainloop, CollectiveEpilogue, void>;
     using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
     using StrideA = typename Kernel::StrideA;

@@ -80,6 +80,7 @@ EXPORTED = [
     "cbm_b200_dense_forward",
     "cbm_b200_dense_forward_relu",
     "cbm_b200_dense_grad_input",
+    "cbm_b200_dense_grad_input_relu",
     "cbm_b200_dense_grad_weight",
     "cbm_b200_dense_grad_weight_workspace",
     "cbm_b200_spmm_update_host",
@@ -205,6 +206,8 @@ def lib() -> ctypes.CDLL:
     sig("cbm_b200_probe_l2_read_gbps", c_double, c_int32)
     for name in ("cbm_b200_dense_forward", "cbm_b200_dense_forward_relu", "cbm_b200_dense_grad_input"):
         sig(name, c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p)
+    sig("cbm_b200_dense_grad_input_relu", c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+        c_int32, c_int32, c_int32, c_void_p)
     sig("cbm_b200_dense_grad_weight", c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int32,
         c_int32, c_int32, c_void_p, c_int64, c_void_p)
     sig("cbm_b200_dense_grad_weight_workspace", c_int64, c_int32, c_int32, c_int32)

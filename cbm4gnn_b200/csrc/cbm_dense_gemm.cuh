@@ -52,14 +52,19 @@ struct WithBands<cutlass::gemm::collective::CollectiveMma<
 #define CBM_DENSE_BANDS 3
 #endif
 
-template <class LayoutA, class LayoutB, int TileN, int TileK, bool Relu = false>
+template <class LayoutA, class LayoutB, int TileN, int TileK, bool Relu = false, bool MaskByAux = false>
 struct FastGemm {
+    static constexpr bool kMaskByAux = MaskByAux;
     using TileShape = Shape<_128, Int<TileN>, Int<TileK>>;
     using ClusterShape = Shape<_1, _1, _1>;
-    // epilogue: D = acc, or D = max(acc, 0) for the map that feeds the ReLU between two layers
-    using Fusion = cute::conditional_t<Relu,
-                                       cutlass::epilogue::fusion::LinCombEltAct<cutlass::epilogue::thread::ReLu, float, float>,
-                                       cutlass::epilogue::fusion::LinearCombination<float, float>>;
+    // epilogue: D = acc; or D = max(acc, 0) for the map that feeds the ReLU between two layers; or
+    // D = acc where a second row-major operand (the ReLU's output, loaded by TMA) is non-zero and 0
+    // elsewhere, for the input gradient that flows back through that ReLU
+    using Fusion = cute::conditional_t<
+        MaskByAux,
+        cutlass::epilogue::fusion::LinCombDeEltAct<RowMajor, cutlass::epilogue::thread::dReLU, float, float, float>,
+        cute::conditional_t<Relu, cutlass::epilogue::fusion::LinCombEltAct<cutlass::epilogue::thread::ReLu, float, float>,
+                            cutlass::epilogue::fusion::LinearCombination<float, float>>>;
     using CollectiveEpilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, TileShape, ClusterShape,
         cutlass::epilogue::collective::EpilogueTileAuto, float, float, float, RowMajor, 4, float, RowMajor, 4,
@@ -80,7 +85,7 @@ struct FastGemm {
 template <class G>
 int run_gemm(const char* who, int m, int n, int k, int batch, const float* a, int64_t lda, int64_t batch_a,
              const float* b, int64_t ldb, int64_t batch_b, float* d, int64_t ldd, int64_t batch_d, void* workspace,
-             size_t workspace_bytes, cudaStream_t stream) {
+             size_t workspace_bytes, cudaStream_t stream, const float* aux = nullptr, int64_t ldaux = 0) {
     typename G::StrideA sa{};
     typename G::StrideB sb{};
     typename G::StrideD sd{};
@@ -103,6 +108,11 @@ int run_gemm(const char* who, int m, int n, int k, int batch, const float* a, in
                                      {m, n, k, batch},
                                      {a, sa, b, sb},
                                      {{1.0f, 0.0f}, nullptr, sd, d, sd}};
+    if constexpr (G::kMaskByAux) {
+        if (!aux) return cbm::fail(CBM_B200_ERR_ARG, std::string(who) + ": mask operand is NULL");
+        args.epilogue.thread.aux_ptr = aux;
+        get<0>(args.epilogue.thread.dAux) = ldaux;
+    }
     // The TMA descriptors are encoded through the driver API, which wants a context current on the
     // calling thread; a thread that has made no runtime call yet (an autograd worker) has none
     // until the device is set.

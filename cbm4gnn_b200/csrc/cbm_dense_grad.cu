@@ -18,6 +18,8 @@ __global__ void reduce_partials_kernel(const float* __restrict__ part, int parts
 
 using GemmNN = FastGemm<RowMajor, RowMajor, 128, 16>;   // A K-contiguous, B N-contiguous: dY W
 using GemmNN64 = FastGemm<RowMajor, RowMajor, 64, 32>;
+using GemmNNMask = FastGemm<RowMajor, RowMajor, 128, 16, false, true>;  // dY W, zeroed where the ReLU output is 0
+using GemmNN64Mask = FastGemm<RowMajor, RowMajor, 64, 32, false, true>;
 using GemmTN = FastGemm<ColMajor, RowMajor, 128, 16>;   // A M-contiguous, B N-contiguous: dY^T X
 using GemmTN64 = FastGemm<ColMajor, RowMajor, 64, 32>;
 
@@ -44,6 +46,19 @@ extern "C" int cbm_b200_dense_grad_input(const float* dy, int64_t lddy, const fl
     if (n_rows == 0) return CBM_B200_OK;
     return run_either<GemmNN, GemmNN64>(n_in, "dense_grad_input", n_rows, n_in, n_out, 1, dy, lddy, (int64_t)0, w, ldw,
                                         (int64_t)0, dx, lddx, (int64_t)0, (void*)nullptr, (size_t)0, (cudaStream_t)stream);
+}
+
+extern "C" int cbm_b200_dense_grad_input_relu(const float* dy, int64_t lddy, const float* w, int64_t ldw, const float* h,
+                                              int64_t ldh, float* dx, int64_t lddx, int32_t n_rows, int32_t n_in,
+                                              int32_t n_out, void* stream) {
+    if (!dy || !w || !h || !dx || n_rows < 0 || n_in <= 0 || n_out <= 0)
+        return cbm::fail(CBM_B200_ERR_ARG, "dense_grad_input_relu: bad arguments");
+    if (ldh < n_in || ldh % 4 != 0 || (reinterpret_cast<uintptr_t>(h) & 15) != 0)
+        return cbm::fail(CBM_B200_ERR_ARG, "dense_grad_input_relu: h must have 16-byte aligned rows of at least n_in floats");
+    if (n_rows == 0) return CBM_B200_OK;
+    return run_either<GemmNNMask, GemmNN64Mask>(n_in, "dense_grad_input_relu", n_rows, n_in, n_out, 1, dy, lddy, (int64_t)0, w,
+                                                ldw, (int64_t)0, dx, lddx, (int64_t)0, (void*)nullptr, (size_t)0,
+                                                (cudaStream_t)stream, h, ldh);
 }
 
 extern "C" int64_t cbm_b200_dense_grad_weight_workspace(int32_t n_rows, int32_t n_in, int32_t n_out) {

@@ -71,8 +71,10 @@ def dense_forward(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = N
     return y
 
 
-def dense_grad_input(gy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """``gy @ w`` for ``gy`` [N, out], ``w`` [out, in]."""
+def dense_grad_input(gy: torch.Tensor, w: torch.Tensor, relu_output: torch.Tensor | None = None) -> torch.Tensor:
+    """``gy @ w`` for ``gy`` [N, out], ``w`` [out, in].  With ``relu_output`` [N, in] (the output of
+    the ReLU this gradient flows back through) the result is zeroed where that output is zero, in
+    the GEMM's epilogue."""
     n, n_out, n_in = gy.size(0), gy.size(1), w.size(1)
     ip, op = _pad4(n_in), _pad4(n_out)
     ga = _widen(gy, op)
@@ -83,8 +85,14 @@ def dense_grad_input(gy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         wa = wp
     gx = torch.empty((n, ip), dtype=gy.dtype, device=gy.device)
     with torch.cuda.device(gy.device):
-        _lib.check(_lib.lib().cbm_b200_dense_grad_input(ga.data_ptr(), ga.stride(0), wa.data_ptr(), wa.stride(0), gx.data_ptr(),
-                                                        gx.stride(0), n, ip, op, _stream(gy)))
+        if relu_output is None:
+            _lib.check(_lib.lib().cbm_b200_dense_grad_input(ga.data_ptr(), ga.stride(0), wa.data_ptr(), wa.stride(0),
+                                                            gx.data_ptr(), gx.stride(0), n, ip, op, _stream(gy)))
+        else:
+            ha = _widen(relu_output, ip)
+            _lib.check(_lib.lib().cbm_b200_dense_grad_input_relu(ga.data_ptr(), ga.stride(0), wa.data_ptr(), wa.stride(0),
+                                                                 ha.data_ptr(), ha.stride(0), gx.data_ptr(), gx.stride(0),
+                                                                 n, ip, op, _stream(gy)))
     return gx[:, :n_in]
 
 
@@ -150,6 +158,39 @@ def linear_relu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if x.dtype != torch.float32 or weight.dtype != torch.float32:
         raise RuntimeError("dense map: fp32 operands expected")
     return _DenseMapRelu.apply(x, weight)
+
+
+class _ReluMapThenMap(torch.autograd.Function):
+    """``relu(p @ w1.T) @ w2.T``: the dense map that ends one layer, the ReLU between two layers and
+    the dense map that opens the next one.  Forward: the ReLU in the first map's epilogue.
+    Backward: the ReLU's mask in the epilogue of the second map's input gradient, so the hidden
+    activations are never passed over by an elementwise kernel in either direction."""
+
+    @staticmethod
+    def forward(ctx, p, w1, w2):
+        h = dense_forward(p, w1, relu=True)
+        ctx.save_for_backward(p, w1, w2, h)
+        return dense_forward(h, w2)
+
+    @staticmethod
+    def backward(ctx, gu):
+        p, w1, w2, h = ctx.saved_tensors
+        gw2 = dense_grad_weight(gu, h) if ctx.needs_input_grad[2] else None
+        gp = gw1 = None
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            gz = dense_grad_input(gu, w2, relu_output=h)  # gradient at the first map's output, before its ReLU
+            gp = dense_grad_input(gz, w1) if ctx.needs_input_grad[0] else None
+            gw1 = dense_grad_weight(gz, p) if ctx.needs_input_grad[1] else None
+        return gp, gw1, gw2
+
+
+def relu_linear_linear(p: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """``relu(p @ w1.T) @ w2.T`` in fp32 accuracy, differentiable in all three arguments."""
+    if not p.is_cuda:
+        return torch.nn.functional.linear(torch.nn.functional.linear(p, w1).relu(), w2)
+    if p.dtype != torch.float32 or w1.dtype != torch.float32 or w2.dtype != torch.float32:
+        raise RuntimeError("dense map: fp32 operands expected")
+    return _ReluMapThenMap.apply(p, w1, w2)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .dense import linear, linear_relu
+from .dense import linear, linear_relu, relu_linear_linear
 from .message_passing import CBMCudaMessagePassing
 
 
@@ -47,6 +47,10 @@ class CBMCudaGCN(CBMCudaMessagePassing):
 
     def product_width(self) -> int:
         return self.in_channels if self.propagate_first() else self.out_channels
+
+    def propagate_only(self, x, edge_index):
+        """The layer's sparse half alone: ``A_hat @ x``."""
+        return CBMCudaMessagePassing.forward(self, edge_index, x=x)
 
     def forward(self, x, edge_index, relu: bool = False):
         """``relu``: apply the ReLU that follows this layer in a stack; when the dense map comes
@@ -96,7 +100,22 @@ class GCNModel(nn.Module):
             layer.cached_a_t = structure
 
     def forward(self, x, edge_index):
+        """Where a layer that propagates first is followed by one that propagates last, the two dense
+        maps and the ReLU between them are adjacent — ``A (relu((A x) W1^T) W2^T)`` — and run as one
+        differentiable step (``relu_linear_linear``)."""
         last = len(self.layers) - 1
-        for i, layer in enumerate(self.layers):
+        i = 0
+        while i <= last:
+            layer = self.layers[i]
+            nxt = self.layers[i + 1] if i < last else None
+            if nxt is not None and x.is_cuda and layer.propagate_first() and not nxt.propagate_first():
+                p = layer.propagate_only(x, edge_index)
+                u = relu_linear_linear(p, layer.lin.weight, nxt.lin.weight)
+                x = nxt.propagate_only(u, edge_index)
+                if i + 1 < last:
+                    x = x.relu()
+                i += 2
+                continue
             x = layer(x, edge_index, relu=i < last)
+            i += 1
         return x

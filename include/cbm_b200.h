@@ -229,6 +229,8 @@ int cbm_b200_selftest_wait(int32_t device, int32_t wait_ms, void* stream);
  *   cbm_b200_dense_forward_relu y = max(x * w^T, 0): the map followed by the ReLU that sits between two
  *                               layers (benchmark/parallel/benchmark_gcn_cpu.py:70-89), in the epilogue
  *   cbm_b200_dense_grad_input   dx [n_rows,n_in] = dy [n_rows,n_out] * w
+ *   cbm_b200_dense_grad_input_relu  the same, set to 0 wherever h [n_rows,n_in] is 0: the gradient that
+ *                               flows back through the ReLU whose output h was (the mask in the epilogue)
  *   cbm_b200_dense_grad_weight  dw [n_out,n_in]  = dy^T * x; contracts over the rows in up to
  *                               CBM_B200_DENSE_MAX_CHUNKS independent chunks whose partial results
  *                               are summed in a fixed order; `workspace` [dev] must hold
@@ -241,6 +243,9 @@ int cbm_b200_dense_forward_relu(const float* x, int64_t ldx, const float* w, int
                                 int64_t ldy, int32_t n_rows, int32_t n_in, int32_t n_out, void* stream);
 int cbm_b200_dense_grad_input(const float* dy, int64_t lddy, const float* w, int64_t ldw, float* dx,
                               int64_t lddx, int32_t n_rows, int32_t n_in, int32_t n_out, void* stream);
+int cbm_b200_dense_grad_input_relu(const float* dy, int64_t lddy, const float* w, int64_t ldw, const float* h,
+                                   int64_t ldh, float* dx, int64_t lddx, int32_t n_rows, int32_t n_in,
+                                   int32_t n_out, void* stream);
 int64_t cbm_b200_dense_grad_weight_workspace(int32_t n_rows, int32_t n_in, int32_t n_out);
 int cbm_b200_dense_grad_weight(const float* dy, int64_t lddy, const float* x, int64_t ldx, float* dw,
                                int64_t lddw, int32_t n_rows, int32_t n_in, int32_t n_out,

@@ -69,3 +69,55 @@ def test_relu_in_the_epilogue():
     out = torch.empty((30_000, 47), device="cuda")
     dense.dense_forward(x.detach(), w.detach()[:47], out=out, relu=True)     # ragged width, narrow tiles
     _check(out, (x.detach().double() @ w.detach()[:47].double().t()).clamp_min(0))
+
+
+@pytest.mark.parametrize("n,n_in,n_out", [(235_868, 256, 64), (50_000, 256, 256), (1000, 20, 12), (129, 100, 47), (17, 33, 5)])
+def test_input_gradient_masked_in_the_epilogue(n, n_in, n_out):
+    """`dense_grad_input(gy, w, relu_output=h)` = (gy w) where h is non-zero, 0 elsewhere; the mask
+    is exact (whole elements are kept or dropped), the kept values those of the unmasked map."""
+    g = torch.Generator(device="cuda").manual_seed(n_in + n_out)
+    gy = torch.randn((n, n_out), device="cuda", generator=g)
+    w = torch.randn((n_out, n_in), device="cuda", generator=g) * 0.1
+    h = torch.randn((n, n_in), device="cuda", generator=g).relu()
+    got = dense.dense_grad_input(gy, w, relu_output=h)
+    plain = dense.dense_grad_input(gy, w)
+    assert torch.equal(got, torch.where(h > 0, plain, torch.zeros_like(plain)))
+    _check(got, (gy.double() @ w.double()) * (h > 0))
+    # a window of a wider buffer as the mask operand (row stride larger than the width)
+    wide = torch.zeros((n, n_in + 8), device="cuda")
+    wide[:, 4:4 + n_in] = h
+    assert torch.equal(dense.dense_grad_input(gy, w, relu_output=wide[:, 4:4 + n_in]), got)
+
+
+def test_two_maps_around_a_relu_as_one_step():
+    """`relu_linear_linear` against float64 autograd of the same expression: value and all three
+    gradients, also when the first operand needs no gradient."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    p = torch.randn((30_000, 128), device="cuda", generator=g)
+    w1 = torch.randn((256, 128), device="cuda", generator=g) * 0.1
+    w2 = torch.randn((64, 256), device="cuda", generator=g) * 0.1
+    gu = torch.randn((30_000, 64), device="cuda", generator=g)
+    for p_needs_grad in (True, False):
+        pa = p.clone().requires_grad_(p_needs_grad)
+        a1, a2 = w1.clone().requires_grad_(True), w2.clone().requires_grad_(True)
+        u = dense.relu_linear_linear(pa, a1, a2)
+        u.backward(gu)
+        pr = p.double().requires_grad_(True)
+        r1, r2 = w1.double().requires_grad_(True), w2.double().requires_grad_(True)
+        h64 = pr @ r1.t()
+        # the reference uses the mask the fp32 path saw: elements within rounding of 0 may differ
+        h32 = dense.dense_forward(p, w1)
+        mask = h32 > 0
+        assert ((h64 > 0) != mask).logical_and(h64.abs() > 1e-4).sum().item() == 0
+        ur = (h64 * mask) @ r2.t()
+        ur.backward(gu.double())
+        _check(u.detach(), ur.detach())
+        _check(a1.grad, r1.grad)
+        _check(a2.grad, r2.grad)
+        if p_needs_grad:
+            _check(pa.grad, pr.grad)
+        else:
+            assert pa.grad is None
+    # CPU operands take the torch path
+    pc, c1, c2 = p[:100].cpu(), w1.cpu(), w2.cpu()
+    assert torch.allclose(dense.relu_linear_linear(pc, c1, c2), (pc @ c1.t()).relu() @ c2.t())

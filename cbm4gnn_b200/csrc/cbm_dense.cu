@@ -12,21 +12,19 @@
 // result carries fp32 accuracy (error ~2^-22 relative per product), which the 1e-4 tolerance of the
 // reference's tests needs and single-pass TF32/BF16 does not give.
 //
-// The kernels are instantiations of the CUTLASS sm100 collective builders (TMA loads, none of them
-// a cluster multicast; an input-transform warp group; tcgen05.mma with the accumulator in TMEM;
-// TMA-store epilogue).  The forward and input-gradient maps run as CTA pairs on neighbouring SMs
-// (cluster 2x1x1, cta_group::2: a 256-row tile whose B half each CTA stages and splits only once),
-// the weight gradient as single CTAs (cluster 1x1x1).  The weight gradient contracts over the N rows of the
+// The kernels are instantiations of the CUTLASS sm100 collective builders (TMA loads without
+// cluster multicast — cluster shape 1x1x1 —, an input-transform warp group, tcgen05.mma with the
+// accumulator in TMEM, TMA-store epilogue).  The weight gradient contracts over the N rows of the
 // graph (hundreds of thousands) into a tiny [out,in] result, so it runs as a batched GEMM over row
 // chunks followed by a reduction of the partial results in a fixed order.
 #include "cbm_dense_gemm.cuh"
 
 namespace cbm_dense {
 // wide (128-column) and narrow (64-column) result tiles; A and B K-contiguous: X W^T
-using GemmNT = FastGemm<RowMajor, ColMajor, 128, 16, false, false, true>;
-using GemmNT64 = FastGemm<RowMajor, ColMajor, 64, 32, false, false, true>;
-using GemmNTRelu = FastGemm<RowMajor, ColMajor, 128, 16, true, false, true>;
-using GemmNT64Relu = FastGemm<RowMajor, ColMajor, 64, 32, true, false, true>;
+using GemmNT = FastGemm<RowMajor, ColMajor, 128, 16>;
+using GemmNT64 = FastGemm<RowMajor, ColMajor, 64, 32>;
+using GemmNTRelu = FastGemm<RowMajor, ColMajor, 128, 16, true>;
+using GemmNT64Relu = FastGemm<RowMajor, ColMajor, 64, 32, true>;
 }  // namespace cbm_dense
 
 using namespace cbm_dense;

@@ -25,8 +25,7 @@ using namespace cute;
 using RowMajor = cutlass::layout::RowMajor;
 using ColMajor = cutlass::layout::ColumnMajor;
 
-// D[M,N] = A[M,K] * B[K,N], fp32 in and out, row-major D.  One CTA computes a 128 x TileN tile (a CTA
-// pair a 256 x TileN tile when TwoSm: 3-5 % faster on the forward maps, 2 % on the GCN training step) with
+// D[M,N] = A[M,K] * B[K,N], fp32 in and out, row-major D.  One CTA computes a 128 x TileN tile with
 // the split A operand held in tensor memory where its layout allows (K-contiguous A), else in
 // shared memory.  Measured on B200 (N = 235 868 rows): 128 x 128 x 16 tiles 0.20 ms for 128 -> 256 and
 // 0.18 ms for 256 -> 128 (cuBLAS fp32 SIMT: 0.33 / 0.31 ms); a 64-column result takes 0.10 ms with
@@ -53,16 +52,11 @@ struct WithBands<cutlass::gemm::collective::CollectiveMma<
 #define CBM_DENSE_BANDS 3
 #endif
 
-template <class LayoutA, class LayoutB, int TileN, int TileK, bool Relu = false, bool MaskByAux = false, bool TwoSm = false>
+template <class LayoutA, class LayoutB, int TileN, int TileK, bool Relu = false, bool MaskByAux = false>
 struct FastGemm {
     static constexpr bool kMaskByAux = MaskByAux;
-    // TwoSm: a pair of CTAs on neighbouring SMs computes a 256 x TileN tile with one MMA stream
-    // (cta_group::2); each CTA stages and splits its own 128 rows of A and only half of the B tile.
-    using TileShape = Shape<Int<TwoSm ? 256 : 128>, Int<TileN>, Int<TileK>>;
-    using ClusterShape = Shape<Int<TwoSm ? 2 : 1>, _1, _1>;
-    using EpilogueSchedule = cute::conditional_t<TwoSm, cutlass::epilogue::TmaWarpSpecialized2Sm, cutlass::epilogue::TmaWarpSpecialized1Sm>;
-    using MainloopSchedule = cute::conditional_t<TwoSm, cutlass::gemm::KernelTmaWarpSpecialized2SmFastFP32Sm100,
-                                                 cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>;
+    using TileShape = Shape<_128, Int<TileN>, Int<TileK>>;
+    using ClusterShape = Shape<_1, _1, _1>;
     // epilogue: D = acc; or D = max(acc, 0) for the map that feeds the ReLU between two layers; or
     // D = acc where a second row-major operand (the ReLU's output, loaded by TMA) is non-zero and 0
     // elsewhere, for the input gradient that flows back through that ReLU
@@ -74,12 +68,12 @@ struct FastGemm {
     using CollectiveEpilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, TileShape, ClusterShape,
         cutlass::epilogue::collective::EpilogueTileAuto, float, float, float, RowMajor, 4, float, RowMajor, 4,
-        EpilogueSchedule, Fusion>::CollectiveOp;
+        cutlass::epilogue::TmaWarpSpecialized1Sm, Fusion>::CollectiveOp;
     using BuiltMainloop = typename cutlass::gemm::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, float, TileShape,
         ClusterShape,
         cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename CollectiveEpilogue::SharedStorage))>,
-        MainloopSchedule>::CollectiveOp;
+        cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>::CollectiveOp;
     using CollectiveMainloop = typename WithBands<BuiltMainloop, CBM_DENSE_BANDS>::type;
     using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, CollectiveMainloop, CollectiveEpilogue, void>;
     using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;

@@ -16,10 +16,10 @@ __global__ void reduce_partials_kernel(const float* __restrict__ part, int parts
     out[transpose ? c * ldo + r : r * ldo + c] = s;
 }
 
-using GemmNN = FastGemm<RowMajor, RowMajor, 128, 16, false, false, true>;   // A K-contiguous, B N-contiguous: dY W
-using GemmNN64 = FastGemm<RowMajor, RowMajor, 64, 32, false, false, true>;
-using GemmNNMask = FastGemm<RowMajor, RowMajor, 128, 16, false, true, true>;  // dY W, zeroed where the ReLU output is 0
-using GemmNN64Mask = FastGemm<RowMajor, RowMajor, 64, 32, false, true, true>;
+using GemmNN = FastGemm<RowMajor, RowMajor, 128, 16>;   // A K-contiguous, B N-contiguous: dY W
+using GemmNN64 = FastGemm<RowMajor, RowMajor, 64, 32>;
+using GemmNNMask = FastGemm<RowMajor, RowMajor, 128, 16, false, true>;  // dY W, zeroed where the ReLU output is 0
+using GemmNN64Mask = FastGemm<RowMajor, RowMajor, 64, 32, false, true>;
 using GemmTN = FastGemm<ColMajor, RowMajor, 128, 16>;   // A M-contiguous, B N-contiguous: dY^T X
 using GemmTN64 = FastGemm<ColMajor, RowMajor, 64, 32>;
 
